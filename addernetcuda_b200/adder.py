@@ -1,0 +1,100 @@
+"""Drop-in for the reference's `adder` module (adder.py): `adder2d`, `adder2d_function`, `adder`.
+
+Same names, constructor arguments, attributes and state-dict keys (`adder`, `b`), so the
+reference's resnet20.py, resnet50.py and vgg.py run unchanged on top of it and its checkpoints
+load.  What differs is underneath: `adder2d_function` calls one fused CUDA kernel per direction on
+NCHW tensors instead of unfold + permute + a kernel on column matrices + permute.  The column
+level autograd Function `adder` is kept for code written against adder.py:43-80.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+from torch.autograd import Function
+
+from . import adder_cuda
+
+# Global switch for the one-instruction clamp in the input gradient (see adder_b200.h).
+FAST_CLAMP = False
+
+
+class _Adder2dNCHW(Function):
+    """out = -sum|x_patch - w| with the reference's two surrogate gradients (adder.py:62-80)."""
+
+    @staticmethod
+    def forward(ctx, x, w, stride, padding):
+        x = x.contiguous()
+        w = w.contiguous()
+        ctx.save_for_backward(x, w)
+        ctx.stride, ctx.padding = stride, padding
+        return adder_cuda.forward(x, w, stride, padding)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, w = ctx.saved_tensors
+        grad_out = grad_out.contiguous()
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            gx = adder_cuda.backward_input(grad_out, x, w, ctx.stride, ctx.padding, FAST_CLAMP)
+        if ctx.needs_input_grad[1]:
+            gw = adder_cuda.backward_weight(grad_out, x, w, ctx.stride, ctx.padding, adder_cuda.ETA)
+        return gx, gw, None, None
+
+
+def adder2d_function(X, W, stride=1, padding=0):
+    """Same contract as adder.py:22-41: X[N,Ci,H,W], W[Co,Ci,k,k] -> [N,Co,Ho,Wo], differentiable."""
+    return _Adder2dNCHW.apply(X, W, stride, padding)
+
+
+class adder(Function):
+    """Column-matrix op of adder.py:43-80: `adder.apply(W_col[Co,K], X_col[K,P]) -> [Co,P]`,
+    backward returning (rescaled grad_W_col, grad_X_col)."""
+
+    @staticmethod
+    def forward(ctx, W_col, X_col):
+        W_col = W_col.contiguous()
+        X_col = X_col.contiguous()
+        ctx.save_for_backward(W_col, X_col)
+        output = torch.empty((W_col.size(0), X_col.size(1)), device=W_col.device, dtype=torch.float32)
+        adder_cuda.ADDER_CONV(X_col, W_col, output)
+        return output
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        W_col, X_col = ctx.saved_tensors
+        grad_output = grad_output.contiguous()
+        grad_W_col = torch.zeros_like(W_col)
+        grad_X_col = torch.zeros_like(X_col)
+        adder_cuda.ADDER_BACKWARD(grad_output, X_col, W_col, grad_W_col, grad_X_col)
+        grad_W_col = grad_W_col / grad_W_col.norm(p=2).clamp(min=1e-12) * math.sqrt(W_col.size(1) * W_col.size(0)) / 5
+        return grad_W_col, grad_X_col
+
+
+class adder2d(nn.Module):
+    """adder.py:83-108.  `depth_wise=True` is rejected: the reference allocates [Co,1,k,k] weights for
+    it but its forward ignores the flag, so no caller can rely on it."""
+
+    def __init__(self, input_channel, output_channel, kernel_size, stride=1, padding=0, bias=False,
+                 depth_wise=False):
+        super().__init__()
+        if depth_wise:
+            raise NotImplementedError("depth_wise adder2d is not implemented (nor computed by the reference)")
+        self.stride = stride
+        self.padding = padding
+        self.input_channel = input_channel
+        self.output_channel = output_channel
+        self.kernel_size = kernel_size
+        self.depth_wise = depth_wise
+        self.adder = torch.nn.Parameter(
+            nn.init.normal_(torch.randn(output_channel, input_channel, kernel_size, kernel_size)))
+        self.bias = bias
+        if bias:
+            self.b = torch.nn.Parameter(nn.init.uniform_(torch.zeros(output_channel)))
+
+    def forward(self, x):
+        output = adder2d_function(x, self.adder, self.stride, self.padding)
+        if self.bias:
+            output = output + self.b.unsqueeze(0).unsqueeze(2).unsqueeze(3)
+        return output

@@ -1,0 +1,355 @@
+// Input gradient of the adder convolution on NCHW tensors, with implicit col2im by gathering:
+//   gx[n,ci,y,x] = sum over (co,kh,kw) with (y+pad-kh, x+pad-kw) = S*(ho,wo), 0<=ho<Ho, 0<=wo<Wo of
+//                  clamp(w[co,ci,kh,kw] - x[n,ci,y,x], -1, 1) * g[n,co,ho,wo]
+// This is CONV_BACKWARD's grad_i (adder_cuda/adder.cu:245-246, :266) followed by the col2im that
+// autograd applies for F.unfold (adder.py:32-33), folded into one pass: every input pixel sums
+// the taps that read it, so nothing is accumulated with atomics and the result is deterministic.
+// Taps that fall into the padding are never gathered, which is what col2im's cropping does.
+//
+// Work decomposition.  A CTA owns TCI = CGI*RC input channels and a tile of TI images x TH input
+// rows; a thread owns RC channels x RW input pixels of one row (for stride S > 1 the RW pixels are
+// S apart and share one column parity, so the set of valid taps is the same for all of them).  The
+// thread keeps its RC*RW input values in registers for the whole kernel.  Output channels are
+// streamed in chunks of CKO through a double-buffered shared-memory stage holding the zero-filled
+// patch of g [CKO][TI*G_ROWS][PITCH] and the weights [CKO*k*k][TCI+4] (input channel innermost).
+//
+// FAST variant: clamp(d,-1,1) = 2*sat(d/2 + 1/2) - 1, so with w' = w/2 + 1/2 staged in shared
+// memory and x' = -x/2 in registers a term costs one saturating add and one fused multiply-add;
+// the correction sum(g) over the same taps is the box sum of the channel-summed g patch, which
+// the CTA accumulates on the side.  The exact variant evaluates the formula as written.
+#include "common.cuh"
+#include "kernels.h"
+#include "patch_fill.cuh"
+
+namespace adder {
+
+template <bool FAST>
+__device__ __forceinline__ float gx_term(float wv, float xv) {
+    if (FAST) return __saturatef(wv + xv);                 // wv = w/2+1/2, xv = -x/2
+    return fminf(fmaxf(wv - xv, -1.f), 1.f);
+}
+
+template <int KS, int S, int RW, int RC, bool FAST>
+__global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
+    constexpr int KK = KS * KS;
+    extern __shared__ __align__(16) float smem[];
+    float* const Gs = smem;
+    float* const Wt = smem + 2 * a.gs_stage;
+    float* const G1 = Wt + 2 * a.ws_stage;
+
+    const int tid = threadIdx.x;
+    const int nthreads = blockDim.x;
+    uint32_t tn, th, tw, tnh;
+    a.d_tiles_w.divmod(blockIdx.x, tnh, tw);
+    a.d_tiles_h.divmod(tnh, tn, th);
+    const int n0 = tn * a.TI;
+    const int hi0 = th * a.TH;
+    const int wq0 = tw * (a.SPRC * RW);           // first class-pixel column of the tile (wi = q*S + pw)
+    const int ci0 = blockIdx.y * a.TCI;
+    const int pad = a.g.pad;
+    const int go_r0 = floor_div(hi0 + pad - (KS - 1), S);
+    const int go_c0 = floor_div(wq0 * S + pad - (KS - 1), S);
+
+    uint32_t cig, seg, t2, wsx, pw, ws, img, hr;
+    a.d_segs.divmod(tid, cig, seg);
+    a.d_spr.divmod(seg, t2, wsx);
+    a.d_sprc.divmod(wsx, pw, ws);
+    a.d_th.divmod(t2, img, hr);
+    const bool active = (int)cig < a.CGI;
+    const int n = n0 + img, hi = hi0 + hr;
+    const int q0 = wq0 + ws * RW;                  // class-pixel index of the thread's first pixel
+    const int HW = a.g.H * a.g.W;
+
+    float xv[RC][RW];
+    float acc[RC][RW];
+#pragma unroll
+    for (int c = 0; c < RC; ++c) {
+        const int ci = ci0 + cig * RC + c;
+#pragma unroll
+        for (int j = 0; j < RW; ++j) {
+            const int wi = (q0 + j) * S + pw;
+            const bool ok = active && n < a.g.N && ci < a.g.Ci && hi < a.g.H && wi < a.g.W;
+            const float v = ok ? __ldg(a.x + ((size_t)(n * a.g.Ci + ci) * HW + hi * a.g.W + wi)) : 0.f;
+            xv[c][j] = FAST ? -0.5f * v : v;
+            acc[c][j] = 0.f;
+        }
+    }
+    if (FAST) {
+        for (int e = tid; e < a.g1_size; e += nthreads) G1[e] = 0.f;
+    }
+
+    const int nchunks = ceil_div(a.g.Co, a.CKO);
+    const int w_elems = a.CKO * a.TCI * KK;
+
+    auto fill = [&](int chunk, int stage) {
+        const int coc0 = chunk * a.CKO;
+        fill_patch(Gs + stage * a.gs_stage, a.gout, a.pd, n0, coc0, go_r0, go_c0, a.g.N, a.g.Co, a.g.Ho, a.g.Wo,
+                   tid, nthreads);
+        float* wt = Wt + stage * a.ws_stage;
+        for (int e = tid; e < w_elems; e += nthreads) {
+            uint32_t col, q, cil, tap;
+            a.d_tcikk.divmod(e, col, q);
+            a.d_kk.divmod(q, cil, tap);
+            const int co = coc0 + col, ci = ci0 + cil;
+            const bool ok = (co < a.g.Co) & (ci < a.g.Ci);
+            const float* src = ok ? a.w + ((size_t)(co * a.g.Ci + ci) * KK + tap) : a.w;
+            cp_async4(wt + (col * KK + tap) * a.TCIP + cil, src, ok);
+        }
+    };
+    // FAST: turn the weights this thread copied into w/2 + 1/2 once they have landed.
+    auto scale_weights = [&](int stage) {
+        float* wt = Wt + stage * a.ws_stage;
+        for (int e = tid; e < w_elems; e += nthreads) {
+            uint32_t col, q, cil, tap;
+            a.d_tcikk.divmod(e, col, q);
+            a.d_kk.divmod(q, cil, tap);
+            float* p = wt + (col * KK + tap) * a.TCIP + cil;
+            *p = fmaf(*p, 0.5f, 0.5f);
+        }
+    };
+
+    fill(0, 0);
+    cp_async_commit();
+    for (int c = 0; c < nchunks; ++c) {
+        if (c + 1 < nchunks) {
+            fill(c + 1, (c + 1) & 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        if (FAST) scale_weights(c & 1);
+        __syncthreads();
+        const float* gs = Gs + (c & 1) * a.gs_stage;
+        if (FAST) {
+            for (int e = tid; e < a.g1_size; e += nthreads) {
+                float s = 0.f;
+                for (int col = 0; col < a.CKO; ++col) s += gs[col * a.CH_STRIDE + e];
+                G1[e] += s;
+            }
+        }
+        if (active) {
+            const float* gimg = gs + img * a.pd.ROWS_PITCH;
+            const float* wt = Wt + (c & 1) * a.ws_stage + cig * RC;
+#pragma unroll 1
+            for (int col = 0; col < a.CKO; ++col) {
+                const float* gch = gimg + col * a.CH_STRIDE;
+                const float* wch = wt + col * KK * a.TCIP;
+                if constexpr (S == 1) {
+                    const float* gcol = gch + ws * RW;
+#pragma unroll
+                    for (int kh = 0; kh < KS; ++kh) {
+                        const float* gr = gcol + ((int)hr + KS - 1 - kh) * a.pd.PITCH;
+                        float gv[RW + KS - 1];
+#pragma unroll
+                        for (int i = 0; i < RW + KS - 1; ++i) gv[i] = gr[i];
+#pragma unroll
+                        for (int kw = 0; kw < KS; ++kw) {
+                            const float4 t = *reinterpret_cast<const float4*>(wch + (kh * KS + kw) * a.TCIP);
+                            const float wv[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                            for (int cc = 0; cc < RC; ++cc)
+#pragma unroll
+                                for (int j = 0; j < RW; ++j)
+                                    acc[cc][j] = fmaf(gx_term<FAST>(wv[cc], xv[cc][j]), gv[j + KS - 1 - kw], acc[cc][j]);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int kh = 0; kh < KS; ++kh) {
+                        const int tr = hi + pad - kh;
+                        if (tr % S != 0) continue;
+                        const float* gr = gch + (tr / S - go_r0) * a.pd.PITCH;
+#pragma unroll
+                        for (int kw = 0; kw < KS; ++kw) {
+                            const int tc = (int)pw + pad - kw;
+                            if (tc % S != 0) continue;
+                            const float* gp = gr + (q0 + tc / S - go_c0);
+                            float gv[RW];
+#pragma unroll
+                            for (int j = 0; j < RW; ++j) gv[j] = gp[j];
+                            const float4 t = *reinterpret_cast<const float4*>(wch + (kh * KS + kw) * a.TCIP);
+                            const float wv[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                            for (int cc = 0; cc < RC; ++cc)
+#pragma unroll
+                                for (int j = 0; j < RW; ++j)
+                                    acc[cc][j] = fmaf(gx_term<FAST>(wv[cc], xv[cc][j]), gv[j], acc[cc][j]);
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    if (!active || n >= a.g.N || hi >= a.g.H) return;
+    float box[RW];
+    if (FAST) {
+        // sum of g over the taps of each pixel = box sum of the channel-summed patch
+#pragma unroll
+        for (int j = 0; j < RW; ++j) box[j] = 0.f;
+        const float* g1 = G1 + img * a.pd.ROWS_PITCH;
+#pragma unroll
+        for (int kh = 0; kh < KS; ++kh) {
+            const int tr = hi + pad - kh;
+            if (tr % S != 0) continue;
+            const float* gr = g1 + (tr / S - go_r0) * a.pd.PITCH;
+#pragma unroll
+            for (int kw = 0; kw < KS; ++kw) {
+                const int tc = (int)pw + pad - kw;
+                if (tc % S != 0) continue;
+                const float* gp = gr + (q0 + tc / S - go_c0);
+#pragma unroll
+                for (int j = 0; j < RW; ++j) box[j] += gp[j];
+            }
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < RC; ++c) {
+        const int ci = ci0 + cig * RC + c;
+        if (ci >= a.g.Ci) break;
+        float* o = a.gx + ((size_t)(n * a.g.Ci + ci) * HW + hi * a.g.W);
+#pragma unroll
+        for (int j = 0; j < RW; ++j) {
+            const int wi = (q0 + j) * S + pw;
+            if (wi < a.g.W) {
+                const float v = FAST ? 2.f * acc[c][j] - box[j] : acc[c][j];
+                o[wi] = a.accumulate ? o[wi] + v : v;
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+
+static int largest_divisor_le_mult(int n, int limit, int mult) {
+    for (int d = limit < n ? limit : n; d >= 1; --d)
+        if (n % d == 0 && (d % mult == 0 || d == n)) return d;
+    return n <= limit ? n : mult;
+}
+
+static int pick_pitch_gx(int cols, int segs, int spr, int sprc, int th, int rows, int rw) {
+    int best = cols, best_cost = 1 << 30;
+    for (int pitch = cols; pitch < cols + 33; ++pitch) {
+        int cost = 0;
+        for (int w0 = 0; w0 < segs; w0 += 32) {
+            int cnt[32] = {0};
+            int worst = 0;
+            for (int l = w0; l < w0 + 32 && l < segs; ++l) {
+                const int wsx = l % spr, t2 = l / spr, hr = t2 % th, img = t2 / th;
+                const int addr = (img * rows + hr) * pitch + (wsx % sprc) * rw;
+                const int b = addr & 31;
+                if (++cnt[b] > worst) worst = cnt[b];
+            }
+            cost += worst;
+        }
+        if (cost < best_cost) { best_cost = cost; best = pitch; }
+    }
+    return best;
+}
+
+template <int KS, int S, int RW, int RC, bool FAST>
+static int launch_gx_t(const Geom& g, const float* gout, const float* x, const float* w, float* gx,
+                       int accumulate, const TileHint& hint, cudaStream_t stream) {
+    GxArgs a;
+    a.g = g; a.gout = gout; a.x = x; a.w = w; a.gx = gx; a.accumulate = accumulate;
+    const int cg_max = hint.cg > 0 ? hint.cg : 8;
+    a.CGI = ceil_div(g.Ci, RC) < cg_max ? ceil_div(g.Ci, RC) : cg_max;
+    a.TCI = a.CGI * RC;
+    a.TCIP = a.TCI + 4;
+    const int threads_target = hint.threads > 0 ? hint.threads : 256;
+    int segs_target = threads_target / a.CGI;
+    if (segs_target < 1) segs_target = 1;
+    const int class_px = ceil_div(g.W, S);                 // pixels of one column parity in a row
+    const int sprc_full = ceil_div(class_px, RW);
+    a.SPRC = sprc_full * S <= segs_target ? sprc_full : (segs_target / S > 0 ? segs_target / S : 1);
+    a.SPR = a.SPRC * S;
+    int rows_target = segs_target / a.SPR;
+    if (rows_target < 1) rows_target = 1;
+    if (hint.th > 0) {
+        a.TH = hint.th < g.H ? hint.th : g.H;
+    } else {
+        a.TH = largest_divisor_le_mult(g.H, rows_target, S);
+    }
+    if (a.TH > g.H) a.TH = g.H;
+    a.TI = 1;
+    if (a.TH == g.H) {
+        a.TI = rows_target / a.TH;
+        if (a.TI < 1) a.TI = 1;
+        if (a.TI > g.N) a.TI = g.N;
+        if (a.TI < 1) a.TI = 1;
+    }
+    if (hint.ti > 0) a.TI = hint.ti;
+    a.SEGS = a.TI * a.TH * a.SPR;
+    const int threads = round_up(a.CGI * a.SEGS, 32);
+    if (threads > 256) return ADDER_ERR_INTERNAL;
+    a.tiles_h = ceil_div(g.H, a.TH);
+    a.tiles_w = ceil_div(sprc_full, a.SPRC);
+    if (S > 1 && a.tiles_h > 1 && a.TH % S != 0) return ADDER_ERR_INTERNAL;
+    PatchDims& pd = a.pd;
+    pd.TI = a.TI;
+    pd.ROWS = (S == 1) ? a.TH + KS - 1 : (a.TH + KS - 2) / S + 2;
+    pd.COLS = a.SPRC * RW + (S - 1 + g.pad) / S - floor_div(g.pad - (KS - 1), S);
+    pd.PITCH = pick_pitch_gx(pd.COLS, a.SEGS, a.SPR, a.SPRC, a.TH, pd.ROWS, RW);
+    pd.ROWS_PITCH = pd.ROWS * pd.PITCH;
+    a.CH_STRIDE = a.TI * pd.ROWS_PITCH;
+    a.g1_size = FAST ? a.CH_STRIDE : 0;
+    const int budget_floats = (hint.smem_kb > 0 ? hint.smem_kb : 100) * 1024 / 4;
+    int cko = hint.ck > 0 ? hint.ck : 8;
+    if (cko > g.Co) cko = g.Co;
+    while (cko > 1) {
+        const int need = 2 * (round_up(cko * a.CH_STRIDE, 4) + cko * KS * KS * a.TCIP) + a.g1_size;
+        if (need <= budget_floats) break;
+        --cko;
+    }
+    a.CKO = cko;
+    pd.CH = cko;
+    a.gs_stage = round_up(cko * a.CH_STRIDE, 4);
+    a.ws_stage = cko * KS * KS * a.TCIP;
+    const size_t smem = ((size_t)2 * (a.gs_stage + a.ws_stage) + a.g1_size) * sizeof(float);
+    if (smem > 200 * 1024) return ADDER_ERR_UNSUPPORTED;
+    pd.d_cols = FastDiv(pd.COLS);
+    pd.d_rows = FastDiv(pd.ROWS);
+    pd.d_ti = FastDiv(pd.TI);
+    a.d_tiles_h = FastDiv(a.tiles_h);
+    a.d_tiles_w = FastDiv(a.tiles_w);
+    a.d_segs = FastDiv(a.SEGS);
+    a.d_spr = FastDiv(a.SPR);
+    a.d_sprc = FastDiv(a.SPRC);
+    a.d_th = FastDiv(a.TH);
+    a.d_tcikk = FastDiv(a.TCI * KS * KS);
+    a.d_kk = FastDiv(KS * KS);
+    const long long gxd = (long long)ceil_div(g.N, a.TI) * a.tiles_h * a.tiles_w;
+    const int gyd = ceil_div(g.Ci, a.TCI);
+    if (gxd > 2147483647LL || gyd > 65535) return ADDER_ERR_UNSUPPORTED;
+    auto kern = adder_gx_kernel<KS, S, RW, RC, FAST>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return ADDER_ERR_CUDA;
+    kern<<<dim3((unsigned)gxd, (unsigned)gyd), threads, smem, stream>>>(a);
+    return cudaGetLastError() == cudaSuccess ? ADDER_OK : ADDER_ERR_CUDA;
+}
+
+int launch_gx(const Geom& g, const float* gout, const float* x, const float* w, float* gx, int fast,
+              int accumulate, const TileHint& hint, cudaStream_t stream) {
+    const int class_px = ceil_div(g.W, g.stride);
+    const bool rw7 = (class_px % 8 != 0) && (class_px % 7 == 0);
+#define ADDER_GX_CASE(KS_, S_)                                                                              \
+    if (g.k == KS_ && g.stride == S_) {                                                                     \
+        if (fast)                                                                                           \
+            return rw7 ? launch_gx_t<KS_, S_, 7, 4, true>(g, gout, x, w, gx, accumulate, hint, stream)       \
+                       : launch_gx_t<KS_, S_, 8, 4, true>(g, gout, x, w, gx, accumulate, hint, stream);      \
+        return rw7 ? launch_gx_t<KS_, S_, 7, 4, false>(g, gout, x, w, gx, accumulate, hint, stream)          \
+                   : launch_gx_t<KS_, S_, 8, 4, false>(g, gout, x, w, gx, accumulate, hint, stream);         \
+    }
+    ADDER_GX_CASE(3, 1)
+    ADDER_GX_CASE(3, 2)
+    ADDER_GX_CASE(1, 1)
+    ADDER_GX_CASE(1, 2)
+#undef ADDER_GX_CASE
+    return ADDER_ERR_UNSUPPORTED;
+}
+
+}  // namespace adder

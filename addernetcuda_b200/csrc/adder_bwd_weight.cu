@@ -1,0 +1,402 @@
+// Weight gradient of the adder convolution on NCHW tensors (implicit im2col), with the reference's
+// adaptive rescale fused behind it:
+//   gw[co,ci,kh,kw] = sum_{n,ho,wo} (xpad[n,ci,ho*S+kh,wo*S+kw] - w[co,ci,kh,kw]) * g[n,co,ho,wo]
+//   gw_scaled       = eta * sqrt(Co*Ci*k*k) * gw / max(||gw||_2, 1e-12)
+// (CONV_BACKWARD's grad_w, adder_cuda/adder.cu:247,:267, followed by adder.py:78.)
+//
+// The sum is evaluated as  sum x*g  -  w * sum g : one fused multiply-add per (co,ci,kh,kw,pixel)
+// in the main kernel; the second term needs only a per-channel sum of g and is applied in the
+// finishing kernel.  Padding pixels carry x = 0, so they still contribute -w*g, as in the
+// reference where F.unfold feeds zeros to the kernel.
+//
+// Main kernel.  A CTA owns an output tile of TM = CGO*RM output channels x TCI = CGC*RC input
+// channels x all k*k taps, and one of `splits` contiguous ranges of pixel tiles.  A thread owns
+// RM x RC x k*k accumulators; the PL threads that share an output group split the row segments of
+// each pixel tile between them and are folded together with warp shuffles at the end.  Each CTA
+// writes its partial sums to its own slice of the workspace: no atomics, fixed summation order.
+// Finishing kernels.  (1) sum the slices in double precision, subtract w * sum g, write the
+// unscaled gradient and per-block partial sums of squares; (2) every block adds the partials
+// in the same order, derives the scale and applies it to its part of the gradient.
+#include "common.cuh"
+#include "kernels.h"
+#include "patch_fill.cuh"
+
+namespace adder {
+
+template <int KS, int S, int RW, int RM, int RC>
+__global__ void __launch_bounds__(256, 2) adder_gw_kernel(const GwArgs a) {
+    constexpr int KK = KS * KS;
+    constexpr int XW = (RW - 1) * S + KS;
+    extern __shared__ __align__(16) float smem[];
+    float* const Xs = smem;
+    float* const Gs = smem + 2 * a.xs_stage;
+
+    const int tid = threadIdx.x;
+    const int nthreads = blockDim.x;
+    const int split = blockIdx.x;
+    uint32_t ct_o, ct_c;
+    a.d_ci_tiles.divmod(blockIdx.y, ct_o, ct_c);
+    const int co0 = ct_o * a.TM, ci0 = ct_c * a.TCI;
+
+    uint32_t og, pl, cgc, cgo;
+    a.d_pl.divmod(tid, og, pl);
+    a.d_cgo.divmod(og, cgc, cgo);
+    const bool active = (int)cgc < a.CGC;
+    const bool do_gsum = active && cgc == 0 && ct_c == 0;
+
+    float acc[RM][RC][KK];
+    float gsum[RM];
+#pragma unroll
+    for (int m = 0; m < RM; ++m) {
+        gsum[m] = 0.f;
+#pragma unroll
+        for (int c = 0; c < RC; ++c)
+#pragma unroll
+            for (int t = 0; t < KK; ++t) acc[m][c][t] = 0.f;
+    }
+
+    const int t_begin = split * a.tiles_per_split;
+    int t_end = t_begin + a.tiles_per_split;
+    if (t_end > a.tiles_total) t_end = a.tiles_total;
+
+    auto fill = [&](int tile, int stage) {
+        uint32_t tn, th, tw, tnh;
+        a.d_tiles_w.divmod(tile, tnh, tw);
+        a.d_tiles_h.divmod(tnh, tn, th);
+        const int n0 = tn * a.TI, ho0 = th * a.TH, wo0 = tw * (a.SPR * RW);
+        fill_patch(Xs + stage * a.xs_stage, a.x, a.pdx, n0, ci0, ho0 * S - a.g.pad, wo0 * S - a.g.pad, a.g.N,
+                   a.g.Ci, a.g.H, a.g.W, tid, nthreads);
+        fill_patch(Gs + stage * a.gs_stage, a.gout, a.pdg, n0, co0, ho0, wo0, a.g.N, a.g.Co, a.g.Ho, a.g.Wo, tid,
+                   nthreads);
+    };
+
+    if (t_begin < t_end) {
+        fill(t_begin, 0);
+        cp_async_commit();
+    }
+    for (int t = t_begin; t < t_end; ++t) {
+        const int stage = (t - t_begin) & 1;
+        if (t + 1 < t_end) {
+            fill(t + 1, stage ^ 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (active) {
+            const float* xs = Xs + stage * a.xs_stage + (cgc * RC) * a.XCH_STRIDE;
+            const float* gs = Gs + stage * a.gs_stage + (cgo * RM) * a.GCH_STRIDE;
+#pragma unroll 1
+            for (int seg = pl; seg < a.SEGS; seg += a.PL) {
+                uint32_t t2, ws, img, hr;
+                a.d_spr.divmod(seg, t2, ws);
+                a.d_th.divmod(t2, img, hr);
+                const float* gp = gs + (img * a.TH + hr) * a.pdg.PITCH + ws * RW;
+                float gv[RM][RW];
+#pragma unroll
+                for (int m = 0; m < RM; ++m) {
+                    if (RW % 4 == 0) {
+#pragma unroll
+                        for (int j = 0; j < RW; j += 4) {
+                            const float4 v = *reinterpret_cast<const float4*>(gp + m * a.GCH_STRIDE + j);
+                            gv[m][j] = v.x; gv[m][j + 1] = v.y; gv[m][j + 2] = v.z; gv[m][j + 3] = v.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < RW; ++j) gv[m][j] = gp[m * a.GCH_STRIDE + j];
+                    }
+                }
+                if (do_gsum) {
+#pragma unroll
+                    for (int m = 0; m < RM; ++m) {
+                        float s = 0.f;
+#pragma unroll
+                        for (int j = 0; j < RW; ++j) s += gv[m][j];
+                        gsum[m] += s;
+                    }
+                }
+                const float* xp = xs + (img * a.pdx.ROWS + hr * S) * a.pdx.PITCH + ws * (RW * S);
+#pragma unroll
+                for (int c = 0; c < RC; ++c) {
+#pragma unroll
+                    for (int kh = 0; kh < KS; ++kh) {
+                        const float* xr = xp + c * a.XCH_STRIDE + kh * a.pdx.PITCH;
+                        float xv[XW];
+#pragma unroll
+                        for (int i = 0; i < XW; ++i) xv[i] = xr[i];
+#pragma unroll
+                        for (int kw = 0; kw < KS; ++kw)
+#pragma unroll
+                            for (int m = 0; m < RM; ++m)
+#pragma unroll
+                                for (int j = 0; j < RW; ++j)
+                                    acc[m][c][kh * KS + kw] = fmaf(xv[j * S + kw], gv[m][j], acc[m][c][kh * KS + kw]);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    // fold the PL pixel lanes (PL is a power of two <= 32 and lanes of a group are adjacent)
+    for (int off = a.PL >> 1; off > 0; off >>= 1) {
+#pragma unroll
+        for (int m = 0; m < RM; ++m) {
+            gsum[m] += __shfl_xor_sync(0xffffffffu, gsum[m], off);
+#pragma unroll
+            for (int c = 0; c < RC; ++c)
+#pragma unroll
+                for (int t = 0; t < KK; ++t) acc[m][c][t] += __shfl_xor_sync(0xffffffffu, acc[m][c][t], off);
+        }
+    }
+    if (!active || pl != 0) return;
+    const int CoK = a.g.Co * a.g.Ci * KK;
+    float* part = a.part + (size_t)split * CoK;
+#pragma unroll
+    for (int m = 0; m < RM; ++m) {
+        const int co = co0 + cgo * RM + m;
+        if (co >= a.g.Co) break;
+        if (do_gsum) a.gsum_part[(size_t)split * a.g.Co + co] = gsum[m];
+#pragma unroll
+        for (int c = 0; c < RC; ++c) {
+            const int ci = ci0 + cgc * RC + c;
+            if (ci >= a.g.Ci) break;
+#pragma unroll
+            for (int t = 0; t < KK; ++t) part[(size_t)(co * a.g.Ci + ci) * KK + t] = acc[m][c][t];
+        }
+    }
+}
+
+constexpr int FIN_THREADS = 256;
+
+// gw[i] = sum_s part[s][i] - w[i] * sum_s gsum_part[s][co(i)]; block partial of sum gw^2.
+__global__ void __launch_bounds__(FIN_THREADS) adder_gw_reduce_kernel(const GwFinishArgs a) {
+    __shared__ double red[FIN_THREADS / 32];
+    const int i = blockIdx.x * FIN_THREADS + threadIdx.x;
+    double v = 0.0;
+    if (i < a.CoK) {
+        const int co = i / a.K;
+        double s = 0.0, gs = 0.0;
+        for (int sp = 0; sp < a.splits; ++sp) {
+            s += (double)a.part[(size_t)sp * a.CoK + i];
+            gs += (double)a.gsum_part[(size_t)sp * a.Co + co];
+        }
+        v = s - (double)a.w[i] * gs;
+        const float vf = (float)v;
+        if (a.accumulate) a.gw[i] += vf; else a.gw[i] = vf;
+        v = (double)vf * (double)vf;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int k = 0; k < FIN_THREADS / 32; ++k) t += red[k];
+        a.norm_part[blockIdx.x] = (float)t;
+    }
+}
+
+// Every block sums the same partials in the same order, so all blocks use an identical scale.
+__global__ void __launch_bounds__(FIN_THREADS) adder_gw_scale_kernel(const GwFinishArgs a, int nblocks) {
+    __shared__ float scale_s;
+    if (threadIdx.x < 32) {
+        double t = 0.0;
+        for (int k = threadIdx.x; k < nblocks; k += 32) t += (double)a.norm_part[k];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+        if (threadIdx.x == 0) {
+            const float nrm = (float)sqrt(t);
+            if (a.out_norm != nullptr && blockIdx.x == 0) *a.out_norm = nrm;
+            scale_s = a.eta * sqrtf((float)a.CoK) / fmaxf(nrm, 1e-12f);
+        }
+    }
+    __syncthreads();
+    const int i = blockIdx.x * FIN_THREADS + threadIdx.x;
+    if (i < a.CoK && a.eta > 0.f) a.gw[i] *= scale_s;
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+
+struct GwPlan {
+    GwArgs a;
+    int threads;
+    size_t smem;
+    int fin_blocks;
+    int status;
+};
+
+static int sm_count() {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return 148;
+    return sms;
+}
+
+static int largest_divisor_le(int n, int limit) {
+    for (int d = limit < n ? limit : n; d >= 1; --d)
+        if (n % d == 0) return d;
+    return 1;
+}
+
+template <int KS, int S, int RW, int RM, int RC>
+static GwPlan plan_gw_t(const Geom& g, const TileHint& hint) {
+    GwPlan p;
+    GwArgs& a = p.a;
+    p.status = ADDER_OK;
+    a.g = g;
+    // output tile
+    const int cgo_max = hint.cg > 0 ? hint.cg : (KS == 1 ? 8 : 8);
+    a.CGO = ceil_div(g.Co, RM) < cgo_max ? ceil_div(g.Co, RM) : cgo_max;
+    const int cgc_max = 8;
+    a.CGC = ceil_div(g.Ci, RC) < cgc_max ? ceil_div(g.Ci, RC) : cgc_max;
+    a.TM = a.CGO * RM;
+    a.TCI = a.CGC * RC;
+    const int threads_target = hint.threads > 0 ? hint.threads : 256;
+    int pl = threads_target / (a.CGO * a.CGC);
+    int pl2 = 1;
+    while (pl2 * 2 <= pl && pl2 < 32) pl2 *= 2;
+    a.PL = pl2;
+    p.threads = round_up(a.CGO * a.CGC * a.PL, 32);
+    if (p.threads > 256) { p.status = ADDER_ERR_INTERNAL; return p; }
+    // pixel tile: aim at a few segments per pixel lane
+    int segs_target = a.PL * 4;
+    if (segs_target < 16) segs_target = 16;
+    const int spr_full = ceil_div(g.Wo, RW);
+    a.SPR = spr_full <= segs_target ? spr_full : segs_target;
+    int rows_target = segs_target / a.SPR;
+    if (rows_target < 1) rows_target = 1;
+    if (hint.th > 0) {
+        a.TH = hint.th < g.Ho ? hint.th : g.Ho;
+    } else {
+        const int d = largest_divisor_le(g.Ho, rows_target);
+        a.TH = (2 * d > rows_target || d == g.Ho) ? d : (rows_target < g.Ho ? rows_target : g.Ho);
+    }
+    a.TI = 1;
+    if (a.TH == g.Ho) {
+        a.TI = rows_target / a.TH;
+        if (a.TI < 1) a.TI = 1;
+        if (a.TI > g.N) a.TI = g.N;
+        if (a.TI < 1) a.TI = 1;
+    }
+    if (hint.ti > 0) a.TI = hint.ti;
+    a.SEGS = a.TI * a.TH * a.SPR;
+    PatchDims& px = a.pdx;
+    px.CH = a.TCI; px.TI = a.TI;
+    px.ROWS = (a.TH - 1) * S + KS;
+    px.COLS = (a.SPR * RW - 1) * S + KS;
+    px.PITCH = (KS == 1 && S == 1) ? round_up(px.COLS, 4) : (px.COLS | 1);
+    px.ROWS_PITCH = px.ROWS * px.PITCH;
+    a.XCH_STRIDE = a.TI * px.ROWS_PITCH;
+    PatchDims& pg = a.pdg;
+    pg.CH = a.TM; pg.TI = a.TI;
+    pg.ROWS = a.TH;
+    pg.COLS = a.SPR * RW;
+    pg.PITCH = round_up(pg.COLS, 4) + 4;
+    pg.ROWS_PITCH = pg.ROWS * pg.PITCH;
+    a.GCH_STRIDE = a.TI * pg.ROWS_PITCH;
+    a.xs_stage = round_up(a.TCI * a.XCH_STRIDE, 4);
+    a.gs_stage = round_up(a.TM * a.GCH_STRIDE, 4);
+    p.smem = (size_t)2 * (a.xs_stage + a.gs_stage) * sizeof(float);
+    if (p.smem > 200 * 1024) { p.status = ADDER_ERR_UNSUPPORTED; return p; }
+    a.tiles_h = ceil_div(g.Ho, a.TH);
+    a.tiles_w = ceil_div(spr_full, a.SPR);
+    const long long tiles_total = (long long)ceil_div(g.N, a.TI) * a.tiles_h * a.tiles_w;
+    if (tiles_total > 2147483647LL) { p.status = ADDER_ERR_UNSUPPORTED; return p; }
+    a.tiles_total = (int)tiles_total;
+    a.n_ci_tiles = ceil_div(g.Ci, a.TCI);
+    const int out_tiles = ceil_div(g.Co, a.TM) * a.n_ci_tiles;
+    if (out_tiles > 65535) { p.status = ADDER_ERR_UNSUPPORTED; return p; }
+    const int target_ctas = 2 * sm_count();
+    int splits = ceil_div(target_ctas, out_tiles);
+    if (splits > a.tiles_total) splits = a.tiles_total;
+    if (splits < 1) splits = 1;
+    a.tiles_per_split = ceil_div(a.tiles_total, splits);
+    if (a.tiles_per_split < 1) a.tiles_per_split = 1;
+    a.splits = ceil_div(a.tiles_total, a.tiles_per_split);
+    if (a.splits < 1) a.splits = 1;
+    px.d_cols = FastDiv(px.COLS); px.d_rows = FastDiv(px.ROWS); px.d_ti = FastDiv(px.TI);
+    pg.d_cols = FastDiv(pg.COLS); pg.d_rows = FastDiv(pg.ROWS); pg.d_ti = FastDiv(pg.TI);
+    a.d_tiles_h = FastDiv(a.tiles_h);
+    a.d_tiles_w = FastDiv(a.tiles_w);
+    a.d_spr = FastDiv(a.SPR);
+    a.d_th = FastDiv(a.TH);
+    a.d_pl = FastDiv(a.PL);
+    a.d_cgo = FastDiv(a.CGO);
+    a.d_ci_tiles = FastDiv(a.n_ci_tiles);
+    p.fin_blocks = ceil_div(g.Co * g.Ci * KS * KS, FIN_THREADS);
+    return p;
+}
+
+static GwPlan plan_gw(const Geom& g, const TileHint& hint) {
+    const bool rw7 = (g.Wo % 8 != 0) && (g.Wo % 7 == 0);
+    if (g.k == 3 && g.stride == 1) return rw7 ? plan_gw_t<3, 1, 7, 4, 2>(g, hint) : plan_gw_t<3, 1, 8, 4, 2>(g, hint);
+    if (g.k == 3 && g.stride == 2) return rw7 ? plan_gw_t<3, 2, 7, 4, 2>(g, hint) : plan_gw_t<3, 2, 8, 4, 2>(g, hint);
+    if (g.k == 1 && g.stride == 1) return rw7 ? plan_gw_t<1, 1, 7, 8, 4>(g, hint) : plan_gw_t<1, 1, 8, 8, 4>(g, hint);
+    if (g.k == 1 && g.stride == 2) return rw7 ? plan_gw_t<1, 2, 7, 8, 4>(g, hint) : plan_gw_t<1, 2, 8, 8, 4>(g, hint);
+    GwPlan p;
+    p.status = ADDER_ERR_UNSUPPORTED;
+    return p;
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+size_t gw_workspace_bytes(const Geom& g, const TileHint& hint) {
+    const GwPlan p = plan_gw(g, hint);
+    if (p.status != ADDER_OK) return 0;
+    const size_t CoK = (size_t)g.Co * g.Ci * g.k * g.k;
+    size_t floats = align_up((size_t)p.a.splits * CoK, 64) + align_up((size_t)p.a.splits * g.Co, 64) +
+                    align_up((size_t)p.fin_blocks, 64);
+    return floats * sizeof(float);
+}
+
+template <int KS, int S, int RW, int RM, int RC>
+static int launch_main_t(const GwPlan& p, cudaStream_t stream) {
+    auto kern = adder_gw_kernel<KS, S, RW, RM, RC>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem) != cudaSuccess)
+        return ADDER_ERR_CUDA;
+    const int out_tiles = ceil_div(p.a.g.Co, p.a.TM) * p.a.n_ci_tiles;
+    kern<<<dim3((unsigned)p.a.splits, (unsigned)out_tiles), p.threads, p.smem, stream>>>(p.a);
+    return cudaGetLastError() == cudaSuccess ? ADDER_OK : ADDER_ERR_CUDA;
+}
+
+int launch_gw(const Geom& g, const float* gout, const float* x, const float* w, float* gw, float eta,
+              float* out_norm, int accumulate, void* workspace, size_t workspace_bytes, const TileHint& hint,
+              cudaStream_t stream) {
+    GwPlan p = plan_gw(g, hint);
+    if (p.status != ADDER_OK) return p.status;
+    const size_t need = gw_workspace_bytes(g, hint);
+    if (workspace == nullptr || workspace_bytes < need) return ADDER_ERR_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return ADDER_ERR_ALIGNMENT;
+    const size_t CoK = (size_t)g.Co * g.Ci * g.k * g.k;
+    float* ws = static_cast<float*>(workspace);
+    p.a.gout = gout; p.a.x = x;
+    p.a.part = ws;
+    p.a.gsum_part = ws + align_up((size_t)p.a.splits * CoK, 64);
+    float* norm_part = p.a.gsum_part + align_up((size_t)p.a.splits * g.Co, 64);
+
+    const bool rw7 = (g.Wo % 8 != 0) && (g.Wo % 7 == 0);
+    int st = ADDER_ERR_UNSUPPORTED;
+    if (g.k == 3 && g.stride == 1) st = rw7 ? launch_main_t<3, 1, 7, 4, 2>(p, stream) : launch_main_t<3, 1, 8, 4, 2>(p, stream);
+    else if (g.k == 3 && g.stride == 2) st = rw7 ? launch_main_t<3, 2, 7, 4, 2>(p, stream) : launch_main_t<3, 2, 8, 4, 2>(p, stream);
+    else if (g.k == 1 && g.stride == 1) st = rw7 ? launch_main_t<1, 1, 7, 8, 4>(p, stream) : launch_main_t<1, 1, 8, 8, 4>(p, stream);
+    else if (g.k == 1 && g.stride == 2) st = rw7 ? launch_main_t<1, 2, 7, 8, 4>(p, stream) : launch_main_t<1, 2, 8, 8, 4>(p, stream);
+    if (st != ADDER_OK) return st;
+
+    GwFinishArgs f;
+    f.part = p.a.part; f.gsum_part = p.a.gsum_part; f.w = w; f.gw = gw; f.norm_part = norm_part;
+    f.out_norm = out_norm; f.CoK = (int)CoK; f.K = g.Ci * g.k * g.k; f.Co = g.Co; f.splits = p.a.splits;
+    f.accumulate = accumulate; f.eta = eta;
+    adder_gw_reduce_kernel<<<p.fin_blocks, FIN_THREADS, 0, stream>>>(f);
+    if (cudaGetLastError() != cudaSuccess) return ADDER_ERR_CUDA;
+    if (eta > 0.f || out_norm != nullptr) {
+        adder_gw_scale_kernel<<<p.fin_blocks, FIN_THREADS, 0, stream>>>(f, p.fin_blocks);
+        if (cudaGetLastError() != cudaSuccess) return ADDER_ERR_CUDA;
+    }
+    return ADDER_OK;
+}
+
+}  // namespace adder

@@ -1,0 +1,275 @@
+// Forward adder convolution on NCHW tensors with implicit im2col:
+//   out[n,co,ho,wo] = - sum_{ci,kh,kw} | xpad[n,ci,ho*S+kh,wo*S+kw] - w[co,ci,kh,kw] |
+// (the reference computes the same sum on a materialised column matrix: adder.py:32-39 feeding
+// the CONV kernel of adder_cuda/adder.cu:19-70).  Padding pixels are zero-valued inputs that
+// still contribute |0 - w|, exactly as F.unfold presents them to the reference kernel.
+//
+// Work decomposition.  A CTA owns TM = CG*RM output channels and a pixel tile of TI images x TH
+// output rows x the full output width.  The pixel tile is cut into row segments of RW consecutive
+// output pixels; a thread owns one segment and RM channels, i.e. an RM x RW register tile.  Input
+// channels are streamed in chunks of CK through a double-buffered shared-memory stage holding
+// the haloed input patch [CK][TI*IN_ROWS][PITCH] and the weight slab [CK*KS*KS][TM+4] (channel
+// innermost, so a thread's RM weights are two 128-bit loads that the whole warp shares).  For
+// each (ci, kh) a thread loads the (RW-1)*S+KS input values its segment touches once and slides
+// the KS taps over them in registers: two FP32 instructions per |x-w| term (subtract, add-abs).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace adder {
+
+template <int KS, int S, int RW, int RM>
+__global__ void __launch_bounds__(256, 2) adder_fwd_kernel(const FwdArgs a) {
+    constexpr int KK = KS * KS;
+    constexpr int XW = (RW - 1) * S + KS;   // input values one segment touches per (ci, kh)
+    extern __shared__ __align__(16) float smem[];
+    float* const Xs = smem;
+    float* const Ws = smem + 2 * a.xs_stage;
+
+    const int tid = threadIdx.x;
+    const int nthreads = blockDim.x;
+    uint32_t tn, th, tw, tnh;
+    a.d_tiles_w.divmod(blockIdx.x, tnh, tw);
+    a.d_tiles_h.divmod(tnh, tn, th);
+    const int n0 = tn * a.TI;
+    const int ho0 = th * a.TH;
+    const int wo_t0 = tw * (a.SPR * RW);      // first output column of this tile
+    const int wi0 = wo_t0 * S - a.g.pad;      // input column of patch column 0
+    const int co0 = blockIdx.y * (a.CG * RM);
+    const int hi0 = ho0 * S - a.g.pad;       // input row of patch row 0
+
+    // thread role: (channel group, segment); segment -> (image, tile row, segment within row)
+    uint32_t cg, seg, t2, ws, img, hr;
+    a.d_segs.divmod(tid, cg, seg);
+    a.d_spr.divmod(seg, t2, ws);
+    a.d_th.divmod(t2, img, hr);
+    const bool active = (int)cg < a.CG;
+    const int xoff = (img * a.IN_ROWS + hr * S) * a.PITCH + ws * (RW * S);
+
+    float acc[RM][RW];
+#pragma unroll
+    for (int m = 0; m < RM; ++m)
+#pragma unroll
+        for (int j = 0; j < RW; ++j) acc[m][j] = 0.f;
+
+    const int K = a.g.Ci * KK;
+    const int HW = a.g.H * a.g.W;
+    const int nchunks = ceil_div(a.g.Ci, a.CK);
+    const int x_elems = a.CK * a.TI * a.IN_ROWS * a.IN_COLS;
+    const int w_elems = a.wkk_pad * a.TM;      // wkk_pad = round_up(CK*KK, 8)
+
+    auto fill = [&](int chunk, int stage) {
+        const int ci0 = chunk * a.CK;
+        float* xs = Xs + stage * a.xs_stage;
+        for (int e = tid; e < x_elems; e += nthreads) {
+            uint32_t rho, c, rho2, r, cil, im;
+            a.d_incols.divmod(e, rho, c);
+            a.d_inrows.divmod(rho, rho2, r);
+            a.d_ti.divmod(rho2, cil, im);
+            const int n = n0 + im, ci = ci0 + cil, hi = hi0 + (int)r, wi = wi0 + (int)c;
+            const bool ok = (n < a.g.N) & (ci < a.g.Ci) & (hi >= 0) & (hi < a.g.H) & (wi >= 0) & (wi < a.g.W);
+            const float* src = ok ? a.x + ((size_t)(n * a.g.Ci + ci) * HW + hi * a.g.W + wi) : a.x;
+            cp_async4(xs + (cil * a.TI + im) * a.ROWS_PITCH + r * a.PITCH + c, src, ok);
+        }
+        float* wsm = Ws + stage * a.ws_stage;
+        const int kbase = ci0 * KK;
+        const int kk_lim = a.CK * KK;
+        for (int e = tid; e < w_elems; e += nthreads) {
+            uint32_t t, col, kkb;
+            const int kk8 = e & 7;
+            t = e >> 3;
+            a.d_tm.divmod(t, kkb, col);
+            const int kk = kkb * 8 + kk8;
+            const int co = co0 + col;
+            const bool ok = (co < a.g.Co) & (kk < kk_lim) & (kbase + kk < K);
+            const float* src = ok ? a.w + ((size_t)co * K + kbase + kk) : a.w;
+            cp_async4(wsm + kk * a.TMP + col, src, ok);
+        }
+    };
+
+    fill(0, 0);
+    cp_async_commit();
+    for (int c = 0; c < nchunks; ++c) {
+        if (c + 1 < nchunks) {
+            fill(c + 1, (c + 1) & 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (active) {
+            const float* xs = Xs + (c & 1) * a.xs_stage + xoff;
+            const float* wsm = Ws + (c & 1) * a.ws_stage + cg * RM;
+#pragma unroll 1
+            for (int cil = 0; cil < a.CK; ++cil) {
+#pragma unroll
+                for (int kh = 0; kh < KS; ++kh) {
+                    float xv[XW];
+                    const float* xr = xs + cil * a.CH_STRIDE + kh * a.PITCH;
+#pragma unroll
+                    for (int i = 0; i < XW; ++i) xv[i] = xr[i];
+#pragma unroll
+                    for (int kw = 0; kw < KS; ++kw) {
+                        const float* wr = wsm + (cil * KK + kh * KS + kw) * a.TMP;
+                        float wv[RM];
+#pragma unroll
+                        for (int m4 = 0; m4 < RM; m4 += 4) {
+                            const float4 t = *reinterpret_cast<const float4*>(wr + m4);
+                            wv[m4] = t.x; wv[m4 + 1] = t.y; wv[m4 + 2] = t.z; wv[m4 + 3] = t.w;
+                        }
+#pragma unroll
+                        for (int m = 0; m < RM; ++m)
+#pragma unroll
+                            for (int j = 0; j < RW; ++j) acc[m][j] += fabsf(xv[j * S + kw] - wv[m]);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    if (!active) return;
+    const int n = n0 + img, ho = ho0 + hr, wo0 = wo_t0 + ws * RW;
+    if (n >= a.g.N || ho >= a.g.Ho) return;
+    const int HoWo = a.g.Ho * a.g.Wo;
+#pragma unroll
+    for (int m = 0; m < RM; ++m) {
+        const int co = co0 + cg * RM + m;
+        if (co >= a.g.Co) break;
+        float* o = a.out + ((size_t)(n * a.g.Co + co) * HoWo + ho * a.g.Wo + wo0);
+        if (RW % 4 == 0 && a.vec_store) {
+#pragma unroll
+            for (int j = 0; j < RW; j += 4)
+                *reinterpret_cast<float4*>(o + j) = make_float4(-acc[m][j], -acc[m][j + 1], -acc[m][j + 2], -acc[m][j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < RW; ++j)
+                if (wo0 + j < a.g.Wo) o[j] = -acc[m][j];
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side: tile plan + launch
+// ------------------------------------------------------------------------------------------
+
+static int largest_divisor_le(int n, int limit) {
+    for (int d = limit < n ? limit : n; d >= 1; --d)
+        if (n % d == 0) return d;
+    return 1;
+}
+
+// Smallest row pitch >= cols for which the 32 lanes of a warp (consecutive segments) read
+// distinct shared-memory banks as often as possible; the cost is the worst bank multiplicity.
+static int pick_pitch(int cols, int segs, int spr, int th, int in_rows, int seg_step, int row_step) {
+    int best = cols, best_cost = 1 << 30;
+    for (int pitch = cols; pitch < cols + 33; ++pitch) {
+        int cost = 0;
+        for (int w0 = 0; w0 < segs; w0 += 32) {
+            int cnt[32] = {0};
+            int worst = 0;
+            for (int l = w0; l < w0 + 32 && l < segs; ++l) {
+                const int ws = l % spr, t2 = l / spr, hr = t2 % th, img = t2 / th;
+                const int addr = (img * in_rows + hr * row_step) * pitch + ws * seg_step;
+                const int b = addr & 31;
+                if (++cnt[b] > worst) worst = cnt[b];
+            }
+            cost += worst;
+        }
+        if (cost < best_cost) { best_cost = cost; best = pitch; }
+    }
+    return best;
+}
+
+template <int KS, int S, int RW, int RM>
+static int launch_fwd_t(const Geom& g, const float* x, const float* w, float* out, const TileHint& hint,
+                        cudaStream_t stream) {
+    FwdArgs a;
+    a.g = g; a.x = x; a.w = w; a.out = out;
+    const int cg_max = hint.cg > 0 ? hint.cg : 8;
+    a.CG = ceil_div(g.Co, RM) < cg_max ? ceil_div(g.Co, RM) : cg_max;
+    a.TM = a.CG * RM;
+    a.TMP = a.TM + 4;
+    const int threads_target = hint.threads > 0 ? hint.threads : 256;
+    int segs_target = threads_target / a.CG;
+    if (segs_target < 1) segs_target = 1;
+    const int spr_full = ceil_div(g.Wo, RW);   // segments in a full output row
+    a.SPR = spr_full <= segs_target ? spr_full : segs_target;
+    int rows_target = segs_target / a.SPR;
+    if (rows_target < 1) rows_target = 1;
+    if (hint.th > 0) {
+        a.TH = hint.th < g.Ho ? hint.th : g.Ho;
+    } else {
+        const int d = largest_divisor_le(g.Ho, rows_target);
+        a.TH = (2 * d > rows_target || d == g.Ho) ? d : (rows_target < g.Ho ? rows_target : g.Ho);
+    }
+    a.TI = 1;
+    if (a.TH == g.Ho) {
+        a.TI = rows_target / a.TH;
+        if (a.TI < 1) a.TI = 1;
+        if (a.TI > g.N) a.TI = g.N;
+        if (a.TI < 1) a.TI = 1;
+    }
+    if (hint.ti > 0) a.TI = hint.ti;
+    a.SEGS = a.TI * a.TH * a.SPR;
+    int threads = round_up(a.CG * a.SEGS, 32);
+    if (threads > 256) return ADDER_ERR_INTERNAL;
+    a.IN_ROWS = (a.TH - 1) * S + KS;
+    a.IN_COLS = (a.SPR * RW - 1) * S + KS;
+    a.PITCH = pick_pitch(a.IN_COLS, a.SEGS, a.SPR, a.TH, a.IN_ROWS, RW * S, S);
+    a.ROWS_PITCH = a.IN_ROWS * a.PITCH;
+    a.CH_STRIDE = a.TI * a.ROWS_PITCH;
+    // channel chunk: fill the shared-memory budget (two CTAs per SM) without exceeding Ci
+    const int budget_floats = (hint.smem_kb > 0 ? hint.smem_kb : 100) * 1024 / 4;
+    int ck = hint.ck > 0 ? hint.ck : 8;
+    if (ck > g.Ci) ck = g.Ci;
+    while (ck > 1) {
+        const int need = 2 * (round_up(ck * a.CH_STRIDE, 4) + round_up(ck * KS * KS, 8) * a.TMP);
+        if (need <= budget_floats) break;
+        --ck;
+    }
+    a.CK = ck;
+    a.wkk_pad = round_up(a.CK * KS * KS, 8);
+    a.xs_stage = round_up(a.CK * a.CH_STRIDE, 4);
+    a.ws_stage = a.wkk_pad * a.TMP;
+    const size_t smem = (size_t)2 * (a.xs_stage + a.ws_stage) * sizeof(float);
+    if (smem > 200 * 1024) return ADDER_ERR_UNSUPPORTED;
+    a.tiles_h = ceil_div(g.Ho, a.TH);
+    a.tiles_w = ceil_div(spr_full, a.SPR);
+    const int tiles_n = ceil_div(g.N, a.TI);
+    a.d_tiles_h = FastDiv(a.tiles_h);
+    a.d_tiles_w = FastDiv(a.tiles_w);
+    a.d_segs = FastDiv(a.SEGS);
+    a.d_spr = FastDiv(a.SPR);
+    a.d_th = FastDiv(a.TH);
+    a.d_incols = FastDiv(a.IN_COLS);
+    a.d_inrows = FastDiv(a.IN_ROWS);
+    a.d_ti = FastDiv(a.TI);
+    a.d_tm = FastDiv(a.TM);
+    a.vec_store = (RW % 4 == 0) && (g.Wo % RW == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+    const long long gx = (long long)tiles_n * a.tiles_h * a.tiles_w;
+    const int gy = ceil_div(g.Co, a.TM);
+    if (gx > 2147483647LL || gy > 65535) return ADDER_ERR_UNSUPPORTED;
+    auto kern = adder_fwd_kernel<KS, S, RW, RM>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return ADDER_ERR_CUDA;
+    kern<<<dim3((unsigned)gx, (unsigned)gy), threads, smem, stream>>>(a);
+    return cudaGetLastError() == cudaSuccess ? ADDER_OK : ADDER_ERR_CUDA;
+}
+
+int launch_fwd(const Geom& g, const float* x, const float* w, float* out, const TileHint& hint,
+               cudaStream_t stream) {
+    const bool rw7 = (g.Wo % 8 != 0) && (g.Wo % 7 == 0);
+#define ADDER_FWD_CASE(KS_, S_)                                                                  \
+    if (g.k == KS_ && g.stride == S_)                                                            \
+        return rw7 ? launch_fwd_t<KS_, S_, 7, 8>(g, x, w, out, hint, stream)                     \
+                   : launch_fwd_t<KS_, S_, 8, 8>(g, x, w, out, hint, stream);
+    ADDER_FWD_CASE(3, 1)
+    ADDER_FWD_CASE(3, 2)
+    ADDER_FWD_CASE(1, 1)
+    ADDER_FWD_CASE(1, 2)
+#undef ADDER_FWD_CASE
+    return ADDER_ERR_UNSUPPORTED;
+}
+
+}  // namespace adder

@@ -1,0 +1,177 @@
+// extern "C" layer of libadder_b200.so: argument validation, geometry, dispatch to the kernels.
+#include <atomic>
+#include "kernels.h"
+
+using namespace adder;
+
+namespace {
+
+struct HintSlot {
+    std::atomic<int> threads{0}, cg{0}, th{0}, ti{0}, ck{0}, smem_kb{0};
+    TileHint load() const {
+        TileHint h;
+        h.threads = threads.load(std::memory_order_relaxed);
+        h.cg = cg.load(std::memory_order_relaxed);
+        h.th = th.load(std::memory_order_relaxed);
+        h.ti = ti.load(std::memory_order_relaxed);
+        h.ck = ck.load(std::memory_order_relaxed);
+        h.smem_kb = smem_kb.load(std::memory_order_relaxed);
+        return h;
+    }
+};
+HintSlot g_hints[3];
+
+// Validates a layer geometry and fills Geom.  Every tensor must have fewer than 2^31 elements
+// (the kernels index tiles with 32-bit integers and element offsets with 64-bit ones).
+int make_geom(int n, int ci, int h, int wd, int co, int k, int stride, int pad, Geom* g) {
+    if (n < 0 || ci <= 0 || h <= 0 || wd <= 0 || co <= 0 || k <= 0 || stride <= 0 || pad < 0) return ADDER_ERR_BAD_SHAPE;
+    if (h + 2 * pad < k || wd + 2 * pad < k) return ADDER_ERR_BAD_SHAPE;
+    if (!((k == 1 || k == 3) && (stride == 1 || stride == 2))) return ADDER_ERR_UNSUPPORTED;
+    if (pad >= k) return ADDER_ERR_UNSUPPORTED;   // a tap row made only of padding never occurs in the callers
+    g->N = n; g->Ci = ci; g->H = h; g->W = wd; g->Co = co; g->k = k; g->stride = stride; g->pad = pad;
+    g->Ho = (h - k + 2 * pad) / stride + 1;
+    g->Wo = (wd - k + 2 * pad) / stride + 1;
+    const long long lim = 2147483647LL;
+    if ((long long)n * ci * h * wd > lim || (long long)n * co * g->Ho * g->Wo > lim || (long long)co * ci * k * k > lim)
+        return ADDER_ERR_UNSUPPORTED;
+    return ADDER_OK;
+}
+
+int make_col_geom(int K, int P, int Co, Geom* g) {
+    if (K <= 0 || P < 0 || Co <= 0) return ADDER_ERR_BAD_SHAPE;
+    // X[K,P] is an NCHW tensor [1,K,1,P]; W[Co,K] is [Co,K,1,1]; Y[Co,P] is [1,Co,1,P].
+    return make_geom(1, K, 1, P > 0 ? P : 1, Co, 1, 1, 0, g);
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* adder_b200_status_string(int status) {
+    switch (status) {
+        case ADDER_OK: return "ok";
+        case ADDER_ERR_NULL_POINTER: return "null pointer";
+        case ADDER_ERR_BAD_SHAPE: return "bad shape";
+        case ADDER_ERR_UNSUPPORTED: return "unsupported kernel size, stride or extent";
+        case ADDER_ERR_ALIGNMENT: return "misaligned pointer";
+        case ADDER_ERR_WORKSPACE: return "workspace missing or too small";
+        case ADDER_ERR_CUDA: return "CUDA runtime error";
+        case ADDER_ERR_INTERNAL: return "internal tile-planning error";
+        default: return "unknown status";
+    }
+}
+
+int adder_b200_version(void) { return ADDER_B200_VERSION; }
+
+int adder_b200_output_size(int h, int w, int k, int stride, int pad, int* ho, int* wo) {
+    if (ho == nullptr || wo == nullptr) return ADDER_ERR_NULL_POINTER;
+    if (h <= 0 || w <= 0 || k <= 0 || stride <= 0 || pad < 0 || h + 2 * pad < k || w + 2 * pad < k)
+        return ADDER_ERR_BAD_SHAPE;
+    *ho = (h - k + 2 * pad) / stride + 1;
+    *wo = (w - k + 2 * pad) / stride + 1;
+    return ADDER_OK;
+}
+
+int adder_b200_forward(const float* x, const float* w, float* out, int n, int ci, int h, int wd, int co, int k,
+                       int stride, int pad, void* stream) {
+    Geom g;
+    const int st = make_geom(n, ci, h, wd, co, k, stride, pad, &g);
+    if (st != ADDER_OK) return st;
+    if (n == 0) return ADDER_OK;
+    if (x == nullptr || w == nullptr || out == nullptr) return ADDER_ERR_NULL_POINTER;
+    return launch_fwd(g, x, w, out, g_hints[0].load(), static_cast<cudaStream_t>(stream));
+}
+
+int adder_b200_backward_input(const float* grad_out, const float* x, const float* w, float* grad_x, int n, int ci,
+                              int h, int wd, int co, int k, int stride, int pad, int flags, void* stream) {
+    Geom g;
+    const int st = make_geom(n, ci, h, wd, co, k, stride, pad, &g);
+    if (st != ADDER_OK) return st;
+    if (n == 0) return ADDER_OK;
+    if (grad_out == nullptr || x == nullptr || w == nullptr || grad_x == nullptr) return ADDER_ERR_NULL_POINTER;
+    return launch_gx(g, grad_out, x, w, grad_x, (flags & ADDER_FLAG_FAST_CLAMP) != 0,
+                     (flags & ADDER_FLAG_ACCUMULATE) != 0, g_hints[1].load(), static_cast<cudaStream_t>(stream));
+}
+
+size_t adder_b200_backward_weight_workspace_bytes(int n, int ci, int h, int wd, int co, int k, int stride, int pad) {
+    Geom g;
+    if (make_geom(n, ci, h, wd, co, k, stride, pad, &g) != ADDER_OK) return 0;
+    if (n == 0) g.N = 1;
+    return gw_workspace_bytes(g, g_hints[2].load());
+}
+
+int adder_b200_backward_weight(const float* grad_out, const float* x, const float* w, float* grad_w, float eta,
+                               float* out_norm, void* workspace, size_t workspace_bytes, int n, int ci, int h,
+                               int wd, int co, int k, int stride, int pad, int flags, void* stream) {
+    Geom g;
+    const int st = make_geom(n, ci, h, wd, co, k, stride, pad, &g);
+    if (st != ADDER_OK) return st;
+    if (w == nullptr || grad_w == nullptr) return ADDER_ERR_NULL_POINTER;
+    if (n > 0 && (grad_out == nullptr || x == nullptr)) return ADDER_ERR_NULL_POINTER;
+    // An empty batch still defines the gradient (all zeros); the kernels handle N = 0 tiles.
+    return launch_gw(g, grad_out, x, w, grad_w, eta, out_norm, (flags & ADDER_FLAG_ACCUMULATE) != 0, workspace,
+                     workspace_bytes, g_hints[2].load(), static_cast<cudaStream_t>(stream));
+}
+
+int adder_b200_backward(const float* grad_out, const float* x, const float* w, float* grad_x, float* grad_w,
+                        float eta, void* workspace, size_t workspace_bytes, int n, int ci, int h, int wd, int co,
+                        int k, int stride, int pad, int flags, void* stream) {
+    int st = adder_b200_backward_input(grad_out, x, w, grad_x, n, ci, h, wd, co, k, stride, pad, flags, stream);
+    if (st != ADDER_OK) return st;
+    return adder_b200_backward_weight(grad_out, x, w, grad_w, eta, nullptr, workspace, workspace_bytes, n, ci, h, wd,
+                                      co, k, stride, pad, flags & ADDER_FLAG_ACCUMULATE, stream);
+}
+
+int adder_b200_conv_col(const float* x, const float* w, float* y, int K, int P, int Co, void* stream) {
+    Geom g;
+    const int st = make_col_geom(K, P, Co, &g);
+    if (st != ADDER_OK) return st;
+    if (P == 0) return ADDER_OK;
+    if (x == nullptr || w == nullptr || y == nullptr) return ADDER_ERR_NULL_POINTER;
+    return launch_fwd(g, x, w, y, g_hints[0].load(), static_cast<cudaStream_t>(stream));
+}
+
+size_t adder_b200_col_workspace_bytes(int K, int P, int Co) {
+    Geom g;
+    if (make_col_geom(K, P, Co, &g) != ADDER_OK) return 0;
+    return gw_workspace_bytes(g, g_hints[2].load());
+}
+
+int adder_b200_conv_weight_col(const float* grad_y, const float* x, const float* w, float* grad_w, int K, int P,
+                               int Co, void* workspace, size_t workspace_bytes, void* stream) {
+    Geom g;
+    const int st = make_col_geom(K, P, Co, &g);
+    if (st != ADDER_OK) return st;
+    if (P == 0) return ADDER_OK;   // accumulating nothing
+    if (grad_y == nullptr || x == nullptr || w == nullptr || grad_w == nullptr) return ADDER_ERR_NULL_POINTER;
+    return launch_gw(g, grad_y, x, w, grad_w, 0.f, nullptr, 1, workspace, workspace_bytes, g_hints[2].load(),
+                     static_cast<cudaStream_t>(stream));
+}
+
+int adder_b200_conv_input_col(const float* grad_y, const float* x, const float* w, float* grad_i, int K, int P,
+                              int Co, void* stream) {
+    Geom g;
+    const int st = make_col_geom(K, P, Co, &g);
+    if (st != ADDER_OK) return st;
+    if (P == 0) return ADDER_OK;
+    if (grad_y == nullptr || x == nullptr || w == nullptr || grad_i == nullptr) return ADDER_ERR_NULL_POINTER;
+    return launch_gx(g, grad_y, x, w, grad_i, 0, 1, g_hints[1].load(), static_cast<cudaStream_t>(stream));
+}
+
+int adder_b200_backward_col(const float* grad_y, const float* x, const float* w, float* grad_w, float* grad_i,
+                            int K, int P, int Co, void* workspace, size_t workspace_bytes, void* stream) {
+    int st = adder_b200_conv_input_col(grad_y, x, w, grad_i, K, P, Co, stream);
+    if (st != ADDER_OK) return st;
+    return adder_b200_conv_weight_col(grad_y, x, w, grad_w, K, P, Co, workspace, workspace_bytes, stream);
+}
+
+int adder_b200_set_tile_hint(int op, int threads, int channel_groups, int tile_rows, int tile_images,
+                             int chunk_channels, int smem_kb) {
+    if (op < 0 || op > 2) return ADDER_ERR_BAD_SHAPE;
+    HintSlot& s = g_hints[op];
+    s.threads.store(threads); s.cg.store(channel_groups); s.th.store(tile_rows); s.ti.store(tile_images);
+    s.ck.store(chunk_channels); s.smem_kb.store(smem_kb);
+    return ADDER_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,65 @@
+// Shared device/host helpers for the adder-convolution kernels (sm_100a, fp32 SIMT).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace adder {
+
+// Geometry of one adder2d layer on NCHW fp32 tensors (square kernel, symmetric padding):
+// the quantities adder.py:22-31 of the reference derives from X.size() and W.size().
+struct Geom {
+    int N, Ci, H, W, Co, Ho, Wo, k, stride, pad;
+};
+
+// Unsigned division by a runtime constant with one multiply-high and one shift.
+// Exact for every numerator n < 2^31 and divisor 1 <= d < 2^31 (round-up method:
+// m = ceil(2^(32+s) / d) - 2^32 with s = ceil(log2 d); n / d = (umulhi(n, m) + n) >> s).
+struct FastDiv {
+    uint32_t mul, shift, div;
+    FastDiv() : mul(0), shift(0), div(1) {}
+    explicit FastDiv(uint32_t d) : div(d) {
+        uint32_t s = 0;
+        while ((1ull << s) < d) ++s;
+        shift = s;
+        mul = (uint32_t)((((1ull << s) - d) << 32) / d + 1);
+    }
+    __host__ __device__ __forceinline__ uint32_t quot(uint32_t n) const {
+#ifdef __CUDA_ARCH__
+        return (__umulhi(n, mul) + n) >> shift;   // n < 2^31 so the add cannot wrap
+#else
+        return (uint32_t)((((uint64_t)n * mul) >> 32) + n) >> shift;
+#endif
+    }
+    __host__ __device__ __forceinline__ void divmod(uint32_t n, uint32_t& q, uint32_t& r) const {
+        q = quot(n);
+        r = n - q * div;
+    }
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// 4-byte asynchronous global->shared copy; when !valid nothing is read and the word is zeroed.
+__device__ __forceinline__ void cp_async4(float* dst_smem, const float* src, bool valid) {
+    const int sz = valid ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(smem_u32(dst_smem)), "l"(src), "r"(sz));
+}
+// 16-byte variant (both addresses 16-byte aligned).
+__device__ __forceinline__ void cp_async16(float* dst_smem, const float* src, bool valid) {
+    const int sz = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst_smem)), "l"(src), "r"(sz));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__host__ __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
+__host__ __device__ __forceinline__ int round_up(int a, int b) { return ceil_div(a, b) * b; }
+// floor(a / b) for b > 0 and any sign of a.
+__host__ __device__ __forceinline__ int floor_div(int a, int b) {
+    int q = a / b;
+    return (a % b != 0 && (a < 0)) ? q - 1 : q;
+}
+
+}  // namespace adder

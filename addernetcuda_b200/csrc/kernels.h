@@ -1,0 +1,79 @@
+// Internal interface between the C-ABI layer (api.cu) and the kernel translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include "common.cuh"
+#include "patch_fill.cuh"
+#include "../../include/adder_b200.h"
+
+namespace adder {
+
+// Optional overrides of the tile heuristics (0 = choose automatically).  Used for tuning sweeps.
+struct TileHint {
+    int threads = 0;   // CTA size target
+    int cg = 0;        // channel groups per CTA
+    int th = 0;        // tile rows
+    int ti = 0;        // tile images
+    int ck = 0;        // channels per shared-memory stage
+    int smem_kb = 0;   // shared-memory budget per CTA
+};
+
+struct FwdArgs {
+    Geom g;
+    const float* x;
+    const float* w;
+    float* out;
+    int TI, TH, SPR, SEGS, CG, TM, TMP, CK;
+    int IN_ROWS, IN_COLS, PITCH, ROWS_PITCH, CH_STRIDE;
+    int xs_stage, ws_stage, wkk_pad, tiles_h, tiles_w, vec_store;
+    FastDiv d_tiles_h, d_tiles_w, d_segs, d_spr, d_th, d_incols, d_inrows, d_ti, d_tm;
+};
+
+struct GxArgs {
+    Geom g;
+    const float* gout;   // [N,Co,Ho,Wo]
+    const float* x;      // [N,Ci,H,W]
+    const float* w;      // [Co,Ci,k,k]
+    float* gx;           // [N,Ci,H,W]
+    PatchDims pd;        // patch of g staged per output-channel chunk
+    int TI, TH, SPRC, SPR, SEGS, CGI, TCI, TCIP, CKO, CH_STRIDE;
+    int gs_stage, ws_stage, g1_size, tiles_h, tiles_w, accumulate;
+    FastDiv d_tiles_h, d_tiles_w, d_segs, d_spr, d_sprc, d_th, d_tcikk, d_kk;
+};
+
+struct GwArgs {
+    Geom g;
+    const float* gout;
+    const float* x;
+    float* part;         // [splits][Co*K] partial sums of x*g
+    float* gsum_part;    // [splits][Co]   partial sums of g
+    PatchDims pdx;       // haloed input patch [TCI][TI*IN_ROWS][PITCH]
+    PatchDims pdg;       // tile of g          [TM][TI*TH][GP]
+    int TI, TH, SPR, SEGS;        // pixel tile (as in the forward kernel)
+    int CGO, CGC, TM, TCI;        // output tile: TM = CGO*RM channels out, TCI = CGC*RC channels in
+    int PL;                       // pixel lanes: threads that share one output tile and split the segments
+    int XCH_STRIDE, GCH_STRIDE;
+    int xs_stage, gs_stage, tiles_h, tiles_w, tiles_total, splits, tiles_per_split, n_ci_tiles;
+    FastDiv d_tiles_h, d_tiles_w, d_spr, d_th, d_pl, d_cgo, d_ci_tiles;
+};
+
+struct GwFinishArgs {
+    const float* part;
+    const float* gsum_part;
+    const float* w;
+    float* gw;           // [Co*K] result (scaled when eta > 0)
+    float* norm_part;    // [finish blocks] partial sums of squares
+    float* out_norm;     // optional: ||gw||_2 before scaling
+    int CoK, K, Co, splits, accumulate;
+    float eta;
+};
+
+int launch_fwd(const Geom& g, const float* x, const float* w, float* out, const TileHint& hint, cudaStream_t s);
+int launch_gx(const Geom& g, const float* gout, const float* x, const float* w, float* gx, int fast,
+              int accumulate, const TileHint& hint, cudaStream_t s);
+size_t gw_workspace_bytes(const Geom& g, const TileHint& hint);
+int launch_gw(const Geom& g, const float* gout, const float* x, const float* w, float* gw, float eta,
+              float* out_norm, int accumulate, void* workspace, size_t workspace_bytes, const TileHint& hint,
+              cudaStream_t s);
+
+}  // namespace adder

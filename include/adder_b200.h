@@ -1,0 +1,137 @@
+/*
+ * adder_b200.h — C ABI of libadder_b200.so: the adder-convolution hot path of AdderNet
+ * (forward, input gradient, weight gradient with the adaptive rescale) as sm_100a CUDA kernels.
+ *
+ * This is the boundary a host framework binds instead of the pybind11 module `adder_cuda` of
+ * LingYeAI/AdderNetCUDA (adder_cuda/adder_cuda.cpp:88-93).  Plain pointers and sizes only.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer to contiguous fp32 data on the current CUDA device, unless
+ *     stated otherwise; the caller owns every buffer (inputs, outputs, workspace); the library
+ *     neither allocates nor frees device memory;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).  All work is
+ *     enqueued asynchronously on it; no call synchronises the device;
+ *   - every function that can fail returns an int status: ADDER_OK (0) or one of the ADDER_ERR_*
+ *     codes below; nothing is printed and the process is never aborted (the reference prints and
+ *     calls abort() on shapes it cannot tile, adder_cuda/adder.cu:294-297,:436-439);
+ *   - kernels are atomic-free and deterministic: the same inputs give bit-identical outputs;
+ *   - NCHW entry points take the layer geometry as (n, ci, h, w, co, k, stride, pad): batch, input
+ *     channels, input height/width, output channels, square kernel size, stride, symmetric zero
+ *     padding.  Output size is ho = (h - k + 2*pad) / stride + 1 (integer division), wo likewise,
+ *     as in adder.py:26-31.  Supported: k in {1, 3}, stride in {1, 2}, any other extent.
+ */
+#ifndef ADDER_B200_H_
+#define ADDER_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ADDER_B200_VERSION 100
+
+#if defined(__GNUC__)
+#define ADDER_API __attribute__((visibility("default")))
+#else
+#define ADDER_API
+#endif
+
+enum {
+    ADDER_OK = 0,
+    ADDER_ERR_NULL_POINTER = 1,  /* a required pointer is NULL */
+    ADDER_ERR_BAD_SHAPE = 2,     /* non-positive extent, kernel larger than the padded input, ... */
+    ADDER_ERR_UNSUPPORTED = 3,   /* kernel size / stride / extent outside what the kernels cover */
+    ADDER_ERR_ALIGNMENT = 4,     /* a pointer is not aligned as documented */
+    ADDER_ERR_WORKSPACE = 5,     /* workspace missing or smaller than the *_workspace_bytes() answer */
+    ADDER_ERR_CUDA = 6,          /* the CUDA runtime rejected a launch or an attribute */
+    ADDER_ERR_INTERNAL = 7       /* tile planner produced an impossible plan (a bug) */
+};
+
+/* flags for the backward entry points */
+#define ADDER_FLAG_FAST_CLAMP 1  /* input gradient: saturating-add form of clamp(); differs from the
+                                    exact form by about 1e-7 per term */
+#define ADDER_FLAG_ACCUMULATE 2  /* add into the output buffer(s) instead of overwriting them */
+
+/* Human-readable name of a status code (static storage, never NULL). */
+ADDER_API const char* adder_b200_status_string(int status);
+
+/* ADDER_B200_VERSION of the loaded library. */
+ADDER_API int adder_b200_version(void);
+
+/* Output extent of a layer; ADDER_ERR_BAD_SHAPE if the geometry is invalid.
+ * Replaces the size arithmetic of adder2d_function (adder.py:26-31). */
+ADDER_API int adder_b200_output_size(int h, int w, int k, int stride, int pad, int* ho, int* wo);
+
+/* ---- fused NCHW path: what adder2d_function + adder.forward/backward compute ------------- */
+
+/* out[n,co,ho,wo] = -sum_{ci,kh,kw} |xpad[n,ci,ho*s+kh,wo*s+kw] - w[co,ci,kh,kw]|.
+ * x[n,ci,h,w], w[co,ci,k,k] -> out[n,co,ho,wo] (overwritten).
+ * Replaces adder2d_function's unfold/permute glue (adder.py:32-34,38-39), adder.forward
+ * (adder.py:45-60) and ADDER_CONV (adder_cuda/adder_cuda.cpp:37-46, adder.cu:19-70,:274-320). */
+ADDER_API int adder_b200_forward(const float* x, const float* w, float* out, int n, int ci, int h, int wd, int co, int k,
+                       int stride, int pad, void* stream);
+
+/* grad_x[n,ci,y,x] = sum over the taps (co,kh,kw) that read that pixel of
+ *                    clamp(w[co,ci,kh,kw] - x[n,ci,y,x], -1, 1) * grad_out[n,co,ho,wo].
+ * Replaces the grad_i half of ADDER_BACKWARD (adder_cuda.cpp:74-86, adder.cu:245-246,:266) plus
+ * the col2im that autograd runs for adder.py:32-33.  flags: ADDER_FLAG_FAST_CLAMP, _ACCUMULATE. */
+ADDER_API int adder_b200_backward_input(const float* grad_out, const float* x, const float* w, float* grad_x, int n, int ci,
+                              int h, int wd, int co, int k, int stride, int pad, int flags, void* stream);
+
+/* Bytes of scratch the weight-gradient entry points need for this geometry on the current device. */
+ADDER_API size_t adder_b200_backward_weight_workspace_bytes(int n, int ci, int h, int wd, int co, int k, int stride, int pad);
+
+/* grad_w[co,ci,kh,kw] = sum_{n,ho,wo} (xpad - w) * grad_out, then, when eta > 0, the adaptive
+ * rescale grad_w <- eta * sqrt(numel(grad_w)) * grad_w / max(||grad_w||_2, 1e-12) (adder.py:78 with
+ * eta = 0.2).  eta <= 0 leaves the gradient unscaled.  out_norm (optional, may be NULL): receives
+ * ||grad_w||_2 before scaling.  workspace: 256-byte aligned device scratch of at least
+ * adder_b200_backward_weight_workspace_bytes(); contents need not be initialised and are
+ * clobbered.  flags: ADDER_FLAG_ACCUMULATE (only meaningful with eta <= 0).
+ * Replaces the grad_w half of ADDER_BACKWARD / ADDER_CONV_WEIGHT (adder_cuda.cpp:48-59,:74-86,
+ * adder.cu:247,:267) and the rescale line adder.py:78. */
+ADDER_API int adder_b200_backward_weight(const float* grad_out, const float* x, const float* w, float* grad_w, float eta,
+                               float* out_norm, void* workspace, size_t workspace_bytes, int n, int ci, int h,
+                               int wd, int co, int k, int stride, int pad, int flags, void* stream);
+
+/* Both gradients of one layer: adder.backward (adder.py:62-80) in one call. */
+ADDER_API int adder_b200_backward(const float* grad_out, const float* x, const float* w, float* grad_x, float* grad_w,
+                        float eta, void* workspace, size_t workspace_bytes, int n, int ci, int h, int wd, int co,
+                        int k, int stride, int pad, int flags, void* stream);
+
+/* ---- column-matrix path: the reference extension's own entry points ------------------------
+ * Layouts as in adder_cuda/adder.cu:26-30: w[Co,K], x[K,P], y / grad_y[Co,P], grad_w[Co,K],
+ * grad_i[K,P].  Any K, P, Co >= 1 (the reference requires Co and P divisible by 16, 12 or 8). */
+
+/* y = -sum_k |w[co,k] - x[k,p]| (y is overwritten).  ADDER_CONV, adder_cuda.cpp:37-46. */
+ADDER_API int adder_b200_conv_col(const float* x, const float* w, float* y, int K, int P, int Co, void* stream);
+
+/* Scratch bytes for the two column entry points that produce grad_w. */
+ADDER_API size_t adder_b200_col_workspace_bytes(int K, int P, int Co);
+
+/* grad_w += sum_p (x - w) * grad_y (accumulates, as the reference's atomicAdd does).
+ * ADDER_CONV_WEIGHT, adder_cuda.cpp:48-59. */
+ADDER_API int adder_b200_conv_weight_col(const float* grad_y, const float* x, const float* w, float* grad_w, int K, int P,
+                               int Co, void* workspace, size_t workspace_bytes, void* stream);
+
+/* grad_i += sum_co clamp(w - x, -1, 1) * grad_y (accumulates).  ADDER_CONV_INPUT,
+ * adder_cuda.cpp:61-72; computes the formula the reference intends (its own kernel drops the
+ * multiplication by grad_y for w - x < -1, adder.cu:17,:170). */
+ADDER_API int adder_b200_conv_input_col(const float* grad_y, const float* x, const float* w, float* grad_i, int K, int P,
+                              int Co, void* stream);
+
+/* Both of the above in one call.  ADDER_BACKWARD, adder_cuda.cpp:74-86. */
+ADDER_API int adder_b200_backward_col(const float* grad_y, const float* x, const float* w, float* grad_w, float* grad_i,
+                            int K, int P, int Co, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- tuning hook ---------------------------------------------------------------------------
+ * Overrides the tile heuristics of one kernel family for subsequent calls from any thread
+ * (op: 0 forward, 1 input gradient, 2 weight gradient; a value of 0 restores the automatic
+ * choice).  Meant for parameter sweeps; not needed for normal use.  No reference counterpart. */
+ADDER_API int adder_b200_set_tile_hint(int op, int threads, int channel_groups, int tile_rows, int tile_images,
+                             int chunk_channels, int smem_kb);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ADDER_B200_H_ */

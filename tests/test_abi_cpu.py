@@ -1,0 +1,126 @@
+"""The C-ABI library loads without a GPU and exports exactly what include/adder_b200.h declares;
+host-side argument checks of the Python layer."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _declared():
+    text = (ROOT / "include" / "adder_b200.h").read_text()
+    return sorted(set(re.findall(r"ADDER_API\s+[\w\s\*]+?\b(adder_b200_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from addernetcuda_b200 import _lib
+    lib = _lib.load()
+    names = _declared()
+    assert len(names) >= 14
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in the header but not exported"
+    assert sorted(_lib.SIGNATURES.keys()) == names, "ctypes prototypes and header disagree"
+
+
+def test_version_and_status_strings():
+    from addernetcuda_b200 import _lib
+    lib = _lib.load()
+    assert lib.adder_b200_version() == 100
+    assert lib.adder_b200_status_string(0) == b"ok"
+    assert b"workspace" in lib.adder_b200_status_string(5)
+    assert lib.adder_b200_status_string(12345) == b"unknown status"
+
+
+def test_output_size_and_shape_errors():
+    from addernetcuda_b200 import _lib
+    lib = _lib.load()
+    ho, wo = ctypes.c_int(), ctypes.c_int()
+    assert lib.adder_b200_output_size(9, 8, 3, 2, 1, ctypes.byref(ho), ctypes.byref(wo)) == 0
+    assert (ho.value, wo.value) == (5, 4)
+    assert lib.adder_b200_output_size(2, 2, 3, 1, 0, ctypes.byref(ho), ctypes.byref(wo)) == 2   # kernel > input
+    assert lib.adder_b200_output_size(8, 8, 3, 1, 1, None, None) == 1
+    # geometry validation happens before any CUDA call: wrong shapes fail the same way without a GPU
+    assert lib.adder_b200_forward(None, None, None, 1, 0, 8, 8, 4, 3, 1, 1, None) == 2     # Ci = 0
+    assert lib.adder_b200_forward(None, None, None, 1, 4, 8, 8, 4, 5, 1, 2, None) == 3     # k = 5 unsupported
+    assert lib.adder_b200_forward(None, None, None, 1, 4, 8, 8, 4, 3, 1, 1, None) == 1     # null pointers
+    assert lib.adder_b200_forward(None, None, None, 0, 4, 8, 8, 4, 3, 1, 1, None) == 0     # empty batch: no-op
+    assert lib.adder_b200_backward_weight_workspace_bytes(256, 16, 32, 32, 16, 3, 1, 1) > 0
+    assert lib.adder_b200_backward_weight_workspace_bytes(256, 16, 32, 32, 16, 4, 1, 1) == 0
+    assert lib.adder_b200_set_tile_hint(7, 0, 0, 0, 0, 0, 0) == 2
+
+
+def test_cpu_tensors_are_rejected_not_computed():
+    """No CPU fallback: the op refuses CPU tensors with the reference's message (adder_cuda.cpp:33)."""
+    from addernetcuda_b200 import adder_cuda
+    x = torch.randn(2, 3, 8, 8)
+    w = torch.randn(4, 3, 3, 3)
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        adder_cuda.forward(x, w, 1, 1)
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        adder_cuda.ADDER_CONV(torch.randn(27, 10), torch.randn(4, 27), torch.zeros(4, 10))
+
+
+def test_module_surface_matches_reference():
+    """Names, constructor signature, attributes and parameter names of adder.py:83-108."""
+    import inspect
+    from addernetcuda_b200 import adder
+    sig = inspect.signature(adder.adder2d.__init__)
+    assert list(sig.parameters)[1:] == ["input_channel", "output_channel", "kernel_size", "stride", "padding",
+                                        "bias", "depth_wise"]
+    assert [sig.parameters[p].default for p in ("stride", "padding", "bias", "depth_wise")] == [1, 0, False, False]
+    m = adder.adder2d(3, 5, 3, stride=2, padding=1, bias=True)
+    assert set(dict(m.named_parameters())) == {"adder", "b"}
+    assert tuple(m.adder.shape) == (5, 3, 3, 3) and tuple(m.b.shape) == (5,)
+    for attr in ("stride", "padding", "input_channel", "output_channel", "kernel_size", "depth_wise", "bias"):
+        assert hasattr(m, attr)
+    assert list(inspect.signature(adder.adder2d_function).parameters) == ["X", "W", "stride", "padding"]
+    assert hasattr(adder.adder, "apply")
+    with pytest.raises(NotImplementedError):
+        adder.adder2d(4, 4, 3, depth_wise=True)
+    from addernetcuda_b200 import adder_cuda
+    for name in ("ADDER_CONV", "ADDER_CONV_WEIGHT", "ADDER_CONV_INPUT", "ADDER_BACKWARD", "forward", "backward"):
+        assert callable(getattr(adder_cuda, name))
+
+
+def test_state_dict_keys_of_builders():
+    from addernetcuda_b200 import resnet as R
+    n20 = R.resnet20()
+    keys = list(n20.state_dict().keys())
+    assert "layer1.0.conv1.adder" in keys and "layer2.0.downsample.0.adder" in keys and "fc.weight" in keys
+    n_adder = sum(1 for k in keys if k.endswith(".adder"))
+    assert n_adder == 20
+    assert sum(p.numel() for p in n20.parameters()) == 272484
+    with torch.device("meta"):
+        n50 = R.resnet50()
+    assert sum(1 for k in n50.state_dict() if k.endswith(".adder")) == 52
+
+
+@pytest.mark.skipif(not Path("/root/reference/resnet20.py").exists(), reason="reference checkout not present")
+def test_reference_model_files_import_unchanged_on_the_dropin():
+    """resnet20.py / resnet50.py / vgg.py of the reference only `import adder`; with the drop-in
+    registered they build, and their state-dict keys equal this repository's builders'."""
+    import importlib
+    import sys
+    import addernetcuda_b200 as ab
+    from addernetcuda_b200 import resnet as R
+    ab.install_dropin()
+    sys.path.insert(0, "/root/reference")
+    try:
+        for mod in ("resnet20", "resnet50", "vgg"):
+            sys.modules.pop(mod, None)
+        r20 = importlib.import_module("resnet20").resnet20()
+        assert list(r20.state_dict().keys()) == list(R.resnet20().state_dict().keys())
+        with torch.device("meta"):
+            r50 = importlib.import_module("resnet50").resnet50()
+            mine = R.resnet50()
+        assert list(r50.state_dict().keys()) == list(mine.state_dict().keys())
+        assert [tuple(v.shape) for v in r50.state_dict().values()] == [tuple(v.shape) for v in mine.state_dict().values()]
+        with torch.device("meta"):
+            importlib.import_module("vgg").vgg11_bn()
+    finally:
+        sys.path.remove("/root/reference")
+        for mod in ("adder", "adder_cuda", "resnet20", "resnet50", "vgg"):
+            sys.modules.pop(mod, None)

@@ -1,0 +1,187 @@
+"""Parity of the CUDA kernels (called through the C ABI) with the reference outputs and the oracle.
+
+Tolerance: |got - want| <= 1e-4 + 1e-5 * |want| per element in fp32, the bound the benchmark
+definition states; the maximum absolute error per tensor is printed (run with -s to see it).
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import adder_oracle as O
+from tests.cases import COL_CASES, LAYER_CASES, draw_cols, draw_layer
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _gpu(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def _assert(ok_msg):
+    ok, worst, msg = ok_msg
+    print("   ", msg)
+    assert ok, msg
+
+
+@pytest.fixture(scope="module")
+def ac():
+    from addernetcuda_b200 import adder_cuda
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    return adder_cuda
+
+
+@pytest.mark.parametrize("case", LAYER_CASES, ids=lambda c: c["name"])
+def test_layer_matches_reference_outputs(case, golden, ac):
+    x, w, g = (_gpu(a) for a in draw_layer(case))
+    s, p = case["stride"], case["pad"]
+    out = ac.forward(x, w, s, p)
+    _assert(golden.check(case["name"], "out", out))
+    gx = ac.backward_input(g, x, w, s, p)
+    _assert(golden.check(case["name"], "grad_x", gx))
+    gx_fast = ac.backward_input(g, x, w, s, p, fast_clamp=True)
+    _assert(golden.check(case["name"], "grad_x", gx_fast))
+    gw = ac.backward_weight(g, x, w, s, p)                        # eta = 0.2, rescaled
+    _assert(golden.check(case["name"], "grad_w", gw))
+    gw_raw, norm = ac.backward_weight(g, x, w, s, p, eta=0.0, return_norm=True)
+    # unscaled sums grow with the number of pixels: compare relative to their own scale
+    want = golden.full(case["name"], "grad_w_unscaled") if golden.has_full(case["name"], "grad_w_unscaled") else None
+    if want is not None:
+        scale = max(1.0, float(np.abs(want).max()))
+        _assert(O.compare("grad_w_unscaled/scale", gw_raw / scale, torch.from_numpy(want) / scale))
+        assert abs(float(norm) - float(np.linalg.norm(want.astype(np.float64)))) <= 1e-5 * float(np.linalg.norm(want)) + 1e-6
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("case", [c for c in LAYER_CASES if c["n"] * c["ci"] * c["co"] * c["h"] * c["w"] <= 1 << 22],
+                         ids=lambda c: c["name"])
+def test_layer_matches_float64_oracle(case, ac):
+    """Against the independent float64 direct form computed now (no stored numbers involved)."""
+    x, w, g = draw_layer(case)
+    s, p = case["stride"], case["pad"]
+    xt, wt, gt = (torch.from_numpy(a) for a in (x, w, g))
+    want_out = O.adder2d_forward_direct(xt, wt, s, p)
+    want_gx, want_gws, _ = O.adder2d_backward_direct(gt, xt, wt, s, p)
+    xg, wg, gg = _gpu(x), _gpu(w), _gpu(g)
+    _assert(O.compare("out", ac.forward(xg, wg, s, p), want_out))
+    _assert(O.compare("grad_x", ac.backward_input(gg, xg, wg, s, p), want_gx))
+    _assert(O.compare("grad_x(fast)", ac.backward_input(gg, xg, wg, s, p, fast_clamp=True), want_gx))
+    _assert(O.compare("grad_w", ac.backward_weight(gg, xg, wg, s, p), want_gws))
+
+
+@pytest.mark.parametrize("case", COL_CASES, ids=lambda c: c["name"])
+def test_reference_extension_entry_points(case, golden, ac):
+    """ADDER_CONV / ADDER_CONV_WEIGHT / ADDER_CONV_INPUT / ADDER_BACKWARD with the reference's
+    argument order and buffer semantics (overwrite y, accumulate into gradients)."""
+    W, X, g = (_gpu(a) for a in draw_cols(case))
+    Co, K = W.shape
+    P = X.shape[1]
+    y = torch.full((Co, P), 7.0, device=DEV)                 # ADDER_CONV must overwrite, not add
+    ac.ADDER_CONV(X, W, y)
+    _assert(golden.check(case["name"], "y", y))
+    gw = torch.zeros((Co, K), device=DEV)
+    gi = torch.zeros((K, P), device=DEV)
+    ac.ADDER_BACKWARD(g, X, W, gw, gi)
+    _assert(golden.check(case["name"], "grad_X", gi))
+    want_gw = golden.full(case["name"], "grad_W_unscaled")
+    scale = max(1.0, float(np.abs(want_gw).max()))
+    _assert(O.compare("grad_W_unscaled/scale", gw / scale, torch.from_numpy(want_gw) / scale))
+    # accumulate semantics: a second call doubles the buffers
+    ac.ADDER_CONV_WEIGHT(g, X, W, gw)
+    ac.ADDER_CONV_INPUT(g, X, W, gi)
+    _assert(O.compare("2*grad_W/scale", gw / scale, 2 * torch.from_numpy(want_gw) / scale))
+    if golden.has_full(case["name"], "grad_X"):
+        _assert(O.compare("2*grad_X", gi, 2 * torch.from_numpy(golden.full(case["name"], "grad_X")), abs_=2e-4))
+    # the column-level autograd Function of adder.py:43-80
+    from addernetcuda_b200 import adder as A
+    Wr, Xr = W.clone().requires_grad_(), X.clone().requires_grad_()
+    A.adder.apply(Wr, Xr).backward(g)
+    _assert(golden.check(case["name"], "grad_W", Wr.grad))
+    _assert(golden.check(case["name"], "grad_X", Xr.grad))
+
+
+def test_module_autograd_and_bias(ac):
+    from addernetcuda_b200 import adder as A
+    from oracle import adder_unfold as U
+    torch.manual_seed(3)
+    m = A.adder2d(5, 7, 3, stride=1, padding=1, bias=True).to(DEV)
+    mo = U.adder2d(5, 7, 3, stride=1, padding=1, bias=True)
+    mo.load_state_dict({k: v.cpu() for k, v in m.state_dict().items()})
+    x = torch.randn(3, 5, 9, 6)
+    xg = x.to(DEV).requires_grad_()
+    xo = x.clone().requires_grad_()
+    yg = m(xg)
+    yo = mo(xo)
+    _assert(O.compare("module out", yg, yo))
+    gy = torch.randn_like(yo)
+    yg.backward(gy.to(DEV))
+    yo.backward(gy)
+    _assert(O.compare("module grad_x", xg.grad, xo.grad))
+    _assert(O.compare("module grad adder", m.adder.grad, mo.adder.grad))
+    _assert(O.compare("module grad b", m.b.grad, mo.b.grad))
+
+
+def test_run_twice_is_bitwise_identical(ac):
+    """The kernels use no atomics: any run-to-run difference would be a race."""
+    case = next(c for c in LAYER_CASES if c["name"].startswith("r20_n4_c16to32_32x32_k3s2"))
+    x, w, g = (_gpu(a) for a in draw_layer(case))
+    s, p = case["stride"], case["pad"]
+    a = [ac.forward(x, w, s, p), ac.backward_input(g, x, w, s, p), ac.backward_weight(g, x, w, s, p)]
+    b = [ac.forward(x, w, s, p), ac.backward_input(g, x, w, s, p), ac.backward_weight(g, x, w, s, p)]
+    for u, v in zip(a, b):
+        assert torch.equal(u, v)
+
+
+def test_no_write_outside_the_outputs(ac):
+    """Outputs are carved out of larger buffers pre-filled with a NaN pattern; after the kernels the
+    guard bands on both sides must be untouched (catches out-of-bounds stores)."""
+    from addernetcuda_b200 import _lib
+    lib = _lib.load()
+    case = next(c for c in LAYER_CASES if c["name"] == "odd_n3_c4to6_9x8_k3s2p1")
+    x, w, g = (_gpu(a) for a in draw_layer(case))
+    n, ci, co, h, wd, k, s, p = (case[q] for q in ("n", "ci", "co", "h", "w", "k", "stride", "pad"))
+    ho, wo = O.out_hw(h, wd, k, s, p)
+    GUARD = 256
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def guarded(numel):
+        buf = torch.full((numel + 2 * GUARD,), float("nan"), device=DEV)
+        return buf, buf[GUARD:GUARD + numel]
+
+    geom = (n, ci, h, wd, co, k, s, p)
+    b_out, v_out = guarded(n * co * ho * wo)
+    assert lib.adder_b200_forward(x.data_ptr(), w.data_ptr(), v_out.data_ptr(), *geom, stream) == 0
+    b_gx, v_gx = guarded(x.numel())
+    assert lib.adder_b200_backward_input(g.data_ptr(), x.data_ptr(), w.data_ptr(), v_gx.data_ptr(), *geom, 0, stream) == 0
+    b_gw, v_gw = guarded(w.numel())
+    nbytes = lib.adder_b200_backward_weight_workspace_bytes(*geom)
+    ws = torch.empty(nbytes + 256, dtype=torch.uint8, device=DEV)
+    assert ws.data_ptr() % 256 == 0
+    assert lib.adder_b200_backward_weight(g.data_ptr(), x.data_ptr(), w.data_ptr(), v_gw.data_ptr(), ctypes.c_float(0.2),
+                                          None, ws.data_ptr(), nbytes, *geom, 0, stream) == 0
+    torch.cuda.synchronize()
+    for buf, view in ((b_out, v_out), (b_gx, v_gx), (b_gw, v_gw)):
+        assert torch.isnan(buf[:GUARD]).all() and torch.isnan(buf[-GUARD:]).all()
+        assert torch.isfinite(view).all()
+    # too-small workspace is refused, not overrun
+    assert lib.adder_b200_backward_weight(g.data_ptr(), x.data_ptr(), w.data_ptr(), v_gw.data_ptr(), ctypes.c_float(0.2),
+                                          None, ws.data_ptr(), 16, *geom, 0, stream) == 5
+
+
+def test_errors_are_statuses_not_aborts(ac):
+    x = torch.randn(2, 3, 8, 8, device=DEV)
+    w = torch.randn(4, 3, 5, 5, device=DEV)
+    with pytest.raises(ValueError):
+        ac.forward(x, w, 1, 2)                      # k = 5: unsupported, reported as an exception
+    with pytest.raises(RuntimeError, match="contiguous"):
+        ac.forward(x.permute(0, 1, 3, 2), torch.randn(4, 3, 3, 3, device=DEV), 1, 1)
+    with pytest.raises(TypeError):
+        ac.forward(x.double(), torch.randn(4, 3, 3, 3, device=DEV).double(), 1, 1)
+    # shapes the reference aborts on (Co, P not multiples of 16/12/8; adder.cu:294-297) just work
+    y = torch.empty(5, 50, device=DEV)
+    ac.ADDER_CONV(torch.randn(27, 50, device=DEV), torch.randn(5, 27, device=DEV), y)
+    assert torch.isfinite(y).all()
+    assert ac.forward(torch.zeros(0, 3, 8, 8, device=DEV), torch.randn(4, 3, 3, 3, device=DEV), 1, 1).shape == (0, 4, 8, 8)
