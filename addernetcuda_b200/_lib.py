@@ -38,6 +38,7 @@ SIGNATURES = {
     "adder_b200_backward_col": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                         c_void_p, c_size_t, c_void_p]),
     "adder_b200_set_tile_hint": (c_int, [c_int] * 7),
+    "adder_b200_describe_plan": (c_int, [c_int, *_GEOM, c_int, c_char_p, c_size_t]),
 }
 
 _lib = None
@@ -67,3 +68,10 @@ def check(status: int, what: str) -> None:
     msg = load().adder_b200_status_string(status).decode()
     exc = ValueError if status in (1, 2, 3, 4, 5) else RuntimeError
     raise exc(f"{what}: {msg} (status {status})")
+
+
+def describe_plan(op: int, n, ci, h, w, co, k, stride, pad, flags: int = 0) -> str:
+    """Tile plan of one kernel family for a layer, as text (launches nothing)."""
+    buf = ctypes.create_string_buffer(512)
+    check(load().adder_b200_describe_plan(op, n, ci, h, w, co, k, stride, pad, flags, buf, 512), "describe_plan")
+    return buf.value.decode()

@@ -25,6 +25,10 @@ class _Adder2dNCHW(Function):
 
     @staticmethod
     def forward(ctx, x, w, stride, padding):
+        # A data-parallel wrapper may attach `_grad_slot` to the parameter: a view into its flat
+        # gradient bucket.  The weight-gradient kernel then writes the rescaled gradient there
+        # directly, so no pack copy precedes the all-reduce.
+        ctx.grad_slot = getattr(w, "_grad_slot", None)
         x = x.contiguous()
         w = w.contiguous()
         ctx.save_for_backward(x, w)
@@ -39,7 +43,8 @@ class _Adder2dNCHW(Function):
         if ctx.needs_input_grad[0]:
             gx = adder_cuda.backward_input(grad_out, x, w, ctx.stride, ctx.padding, FAST_CLAMP)
         if ctx.needs_input_grad[1]:
-            gw = adder_cuda.backward_weight(grad_out, x, w, ctx.stride, ctx.padding, adder_cuda.ETA)
+            gw = adder_cuda.backward_weight(grad_out, x, w, ctx.stride, ctx.padding, adder_cuda.ETA,
+                                            out=ctx.grad_slot)
         return gx, gw, None, None
 
 

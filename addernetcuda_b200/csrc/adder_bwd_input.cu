@@ -20,6 +20,7 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "patch_fill.cuh"
+#include <cstdio>
 
 namespace adder {
 
@@ -36,6 +37,7 @@ __global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
     float* const Gs = smem;
     float* const Wt = smem + 2 * a.gs_stage;
     float* const G1 = Wt + 2 * a.ws_stage;
+    float* const Tot = G1 + a.g1_size + threadIdx.x;   // [RC*RW][blockDim.x] running totals, one column per thread
 
     const int tid = threadIdx.x;
     const int nthreads = blockDim.x;
@@ -179,11 +181,26 @@ __global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
                     }
                 }
             }
+            // Two-level summation: the chunk's partial sums are folded into per-thread running totals
+            // kept in shared memory, so a long sum over output channels loses far less precision than one
+            // running fp32 accumulator would.
+#pragma unroll
+            for (int cc = 0; cc < RC; ++cc)
+#pragma unroll
+                for (int j = 0; j < RW; ++j) {
+                    float* t = Tot + (cc * RW + j) * nthreads;
+                    *t = (c == 0 ? 0.f : *t) + acc[cc][j];
+                    acc[cc][j] = 0.f;
+                }
         }
         __syncthreads();
     }
 
     if (!active || n >= a.g.N || hi >= a.g.H) return;
+#pragma unroll
+    for (int cc = 0; cc < RC; ++cc)
+#pragma unroll
+        for (int j = 0; j < RW; ++j) acc[cc][j] = Tot[(cc * RW + j) * nthreads];
     float box[RW];
     if (FAST) {
         // sum of g over the taps of each pixel = box sum of the channel-summed patch
@@ -251,11 +268,19 @@ static int pick_pitch_gx(int cols, int segs, int spr, int sprc, int th, int rows
     return best;
 }
 
-template <int KS, int S, int RW, int RC, bool FAST>
-static int launch_gx_t(const Geom& g, const float* gout, const float* x, const float* w, float* gx,
-                       int accumulate, const TileHint& hint, cudaStream_t stream) {
+struct GxPlan {
     GxArgs a;
-    a.g = g; a.gout = gout; a.x = x; a.w = w; a.gx = gx; a.accumulate = accumulate;
+    int threads, ks, s, rw, rc, fast;
+    size_t smem;
+    long long gx;
+    int gy;
+};
+
+template <int KS, int S, int RW, int RC, bool FAST>
+static int plan_gx_t(const Geom& g, const TileHint& hint, GxPlan& p) {
+    GxArgs& a = p.a;
+    p.ks = KS; p.s = S; p.rw = RW; p.rc = RC; p.fast = FAST;
+    a.g = g;
     const int cg_max = hint.cg > 0 ? hint.cg : 8;
     a.CGI = ceil_div(g.Ci, RC) < cg_max ? ceil_div(g.Ci, RC) : cg_max;
     a.TCI = a.CGI * RC;
@@ -285,6 +310,7 @@ static int launch_gx_t(const Geom& g, const float* gout, const float* x, const f
     if (hint.ti > 0) a.TI = hint.ti;
     a.SEGS = a.TI * a.TH * a.SPR;
     const int threads = round_up(a.CGI * a.SEGS, 32);
+    p.threads = threads;
     if (threads > 256) return ADDER_ERR_INTERNAL;
     a.tiles_h = ceil_div(g.H, a.TH);
     a.tiles_w = ceil_div(sprc_full, a.SPRC);
@@ -301,7 +327,7 @@ static int launch_gx_t(const Geom& g, const float* gout, const float* x, const f
     int cko = hint.ck > 0 ? hint.ck : 8;
     if (cko > g.Co) cko = g.Co;
     while (cko > 1) {
-        const int need = 2 * (round_up(cko * a.CH_STRIDE, 4) + cko * KS * KS * a.TCIP) + a.g1_size;
+        const int need = 2 * (round_up(cko * a.CH_STRIDE, 4) + cko * KS * KS * a.TCIP) + a.g1_size + RC * RW * threads;
         if (need <= budget_floats) break;
         --cko;
     }
@@ -309,11 +335,11 @@ static int launch_gx_t(const Geom& g, const float* gout, const float* x, const f
     pd.CH = cko;
     a.gs_stage = round_up(cko * a.CH_STRIDE, 4);
     a.ws_stage = cko * KS * KS * a.TCIP;
-    const size_t smem = ((size_t)2 * (a.gs_stage + a.ws_stage) + a.g1_size) * sizeof(float);
+    const size_t smem = ((size_t)2 * (a.gs_stage + a.ws_stage) + a.g1_size + (size_t)RC * RW * threads) * sizeof(float);
+    p.smem = smem;
     if (smem > 200 * 1024) return ADDER_ERR_UNSUPPORTED;
     pd.d_cols = FastDiv(pd.COLS);
     pd.d_rows = FastDiv(pd.ROWS);
-    pd.d_ti = FastDiv(pd.TI);
     a.d_tiles_h = FastDiv(a.tiles_h);
     a.d_tiles_w = FastDiv(a.tiles_w);
     a.d_segs = FastDiv(a.SEGS);
@@ -324,12 +350,47 @@ static int launch_gx_t(const Geom& g, const float* gout, const float* x, const f
     a.d_kk = FastDiv(KS * KS);
     const long long gxd = (long long)ceil_div(g.N, a.TI) * a.tiles_h * a.tiles_w;
     const int gyd = ceil_div(g.Ci, a.TCI);
+    p.gx = gxd; p.gy = gyd;
     if (gxd > 2147483647LL || gyd > 65535) return ADDER_ERR_UNSUPPORTED;
+    return ADDER_OK;
+}
+
+template <int KS, int S, int RW, int RC, bool FAST>
+static int launch_gx_t(const Geom& g, const float* gout, const float* x, const float* w, float* gx,
+                       int accumulate, const TileHint& hint, cudaStream_t stream) {
+    GxPlan p;
+    const int st = plan_gx_t<KS, S, RW, RC, FAST>(g, hint, p);
+    if (st != ADDER_OK) return st;
+    p.a.gout = gout; p.a.x = x; p.a.w = w; p.a.gx = gx; p.a.accumulate = accumulate;
     auto kern = adder_gx_kernel<KS, S, RW, RC, FAST>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem) != cudaSuccess)
         return ADDER_ERR_CUDA;
-    kern<<<dim3((unsigned)gxd, (unsigned)gyd), threads, smem, stream>>>(a);
+    kern<<<dim3((unsigned)p.gx, (unsigned)p.gy), p.threads, p.smem, stream>>>(p.a);
     return cudaGetLastError() == cudaSuccess ? ADDER_OK : ADDER_ERR_CUDA;
+}
+
+int describe_gx(const Geom& g, int fast, const TileHint& hint, char* buf, size_t n) {
+    const int class_px = ceil_div(g.W, g.stride);
+    const bool rw7 = (class_px % 8 != 0) && (class_px % 7 == 0);
+    GxPlan p;
+    int st = ADDER_ERR_UNSUPPORTED;
+#define ADDER_GX_PLAN(KS_, S_)                                                                          \
+    if (g.k == KS_ && g.stride == S_) {                                                                 \
+        if (fast) st = rw7 ? plan_gx_t<KS_, S_, 7, 4, true>(g, hint, p) : plan_gx_t<KS_, S_, 8, 4, true>(g, hint, p); \
+        else st = rw7 ? plan_gx_t<KS_, S_, 7, 4, false>(g, hint, p) : plan_gx_t<KS_, S_, 8, 4, false>(g, hint, p);    \
+    }
+    ADDER_GX_PLAN(3, 1)
+    ADDER_GX_PLAN(3, 2)
+    ADDER_GX_PLAN(1, 1)
+    ADDER_GX_PLAN(1, 2)
+#undef ADDER_GX_PLAN
+    if (st == ADDER_ERR_UNSUPPORTED && !((g.k == 1 || g.k == 3) && (g.stride == 1 || g.stride == 2))) return st;
+    snprintf(buf, n,
+             "gx k=%d s=%d RW=%d RC=%d fast=%d CGI=%d TCI=%d TI=%d TH=%d SPRC=%d SEGS=%d CKO=%d rows=%d cols=%d pitch=%d "
+             "threads=%d smem=%zu grid=(%lld,%d) status=%d",
+             p.ks, p.s, p.rw, p.rc, p.fast, p.a.CGI, p.a.TCI, p.a.TI, p.a.TH, p.a.SPRC, p.a.SEGS, p.a.CKO, p.a.pd.ROWS,
+             p.a.pd.COLS, p.a.pd.PITCH, p.threads, p.smem, p.gx, p.gy, st);
+    return ADDER_OK;
 }
 
 int launch_gx(const Geom& g, const float* gout, const float* x, const float* w, float* gx, int fast,

@@ -15,11 +15,12 @@
 // each pixel tile between them and are folded together with warp shuffles at the end.  Each CTA
 // writes its partial sums to its own slice of the workspace: no atomics, fixed summation order.
 // Finishing kernels.  (1) sum the slices in double precision, subtract w * sum g, write the
-// unscaled gradient and per-block partial sums of squares; (2) every block adds the partials
-// in the same order, derives the scale and applies it to its part of the gradient.
+// unscaled gradient and per-block partial sums of squares; (2) one block adds those partials
+// in a fixed order and derives the scale; (3) the scale is applied to the gradient.
 #include "common.cuh"
 #include "kernels.h"
 #include "patch_fill.cuh"
+#include <cstdio>
 
 namespace adder {
 
@@ -169,52 +170,76 @@ __global__ void __launch_bounds__(256, 2) adder_gw_kernel(const GwArgs a) {
 }
 
 constexpr int FIN_THREADS = 256;
+constexpr int FIN_OUT = 32;                       // gradient elements per reduce block
+constexpr int FIN_LANES = FIN_THREADS / FIN_OUT;  // threads that share one element and split the slices
 
-// gw[i] = sum_s part[s][i] - w[i] * sum_s gsum_part[s][co(i)]; block partial of sum gw^2.
+// gw[i] = sum_s part[s][i] - w[i] * sum_s gsum_part[s][co(i)], plus the block's partial of sum gw^2.
+// Thread (o, lane) adds the slices lane, lane+8, ... in double precision; the 8 lanes of an element
+// are then added in a fixed order, so the result does not depend on scheduling.
 __global__ void __launch_bounds__(FIN_THREADS) adder_gw_reduce_kernel(const GwFinishArgs a) {
-    __shared__ double red[FIN_THREADS / 32];
-    const int i = blockIdx.x * FIN_THREADS + threadIdx.x;
-    double v = 0.0;
+    __shared__ double s_sum[FIN_LANES][FIN_OUT];
+    __shared__ double s_gs[FIN_LANES][FIN_OUT];
+    __shared__ double s_sq[FIN_OUT];
+    const int o = threadIdx.x & (FIN_OUT - 1);
+    const int lane = threadIdx.x / FIN_OUT;
+    const int i = blockIdx.x * FIN_OUT + o;
+    double s = 0.0, gs = 0.0;
     if (i < a.CoK) {
         const int co = i / a.K;
-        double s = 0.0, gs = 0.0;
-        for (int sp = 0; sp < a.splits; ++sp) {
-            s += (double)a.part[(size_t)sp * a.CoK + i];
-            gs += (double)a.gsum_part[(size_t)sp * a.Co + co];
+        const float* p = a.part + i;
+        const float* q = a.gsum_part + co;
+#pragma unroll 4
+        for (int sp = lane; sp < a.splits; sp += FIN_LANES) {
+            s += (double)p[(size_t)sp * a.CoK];
+            gs += (double)q[(size_t)sp * a.Co];
         }
-        v = s - (double)a.w[i] * gs;
-        const float vf = (float)v;
-        if (a.accumulate) a.gw[i] += vf; else a.gw[i] = vf;
-        v = (double)vf * (double)vf;
     }
+    s_sum[lane][o] = s;
+    s_gs[lane][o] = gs;
+    __syncthreads();
+    if (lane == 0) {
+        double v2 = 0.0;
+        if (i < a.CoK) {
+            double t = 0.0, g = 0.0;
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+            for (int l = 0; l < FIN_LANES; ++l) { t += s_sum[l][o]; g += s_gs[l][o]; }
+            const float vf = (float)(t - (double)a.w[i] * g);
+            if (a.accumulate) a.gw[i] += vf; else a.gw[i] = vf;
+            v2 = (double)vf * (double)vf;
+        }
+        s_sq[o] = v2;
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
         double t = 0.0;
-        for (int k = 0; k < FIN_THREADS / 32; ++k) t += red[k];
+        for (int k = 0; k < FIN_OUT; ++k) t += s_sq[k];
         a.norm_part[blockIdx.x] = (float)t;
     }
 }
 
-// Every block sums the same partials in the same order, so all blocks use an identical scale.
-__global__ void __launch_bounds__(FIN_THREADS) adder_gw_scale_kernel(const GwFinishArgs a, int nblocks) {
-    __shared__ float scale_s;
-    if (threadIdx.x < 32) {
-        double t = 0.0;
-        for (int k = threadIdx.x; k < nblocks; k += 32) t += (double)a.norm_part[k];
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
-        if (threadIdx.x == 0) {
-            const float nrm = (float)sqrt(t);
-            if (a.out_norm != nullptr && blockIdx.x == 0) *a.out_norm = nrm;
-            scale_s = a.eta * sqrtf((float)a.CoK) / fmaxf(nrm, 1e-12f);
-        }
-    }
+// One block: adds the per-block partial sums of squares in a fixed order and writes
+// scale = eta * sqrt(numel) / max(||gw||, 1e-12) (and the norm itself, if asked for).
+__global__ void __launch_bounds__(1024) adder_gw_norm_kernel(const GwFinishArgs a, int nblocks, float* scale_out) {
+    __shared__ double red[1024];
+    double t = 0.0;
+    for (int k = threadIdx.x; k < nblocks; k += 1024) t += (double)a.norm_part[k];
+    red[threadIdx.x] = t;
     __syncthreads();
+    for (int off = 512; off > 0; off >>= 1) {
+        if ((int)threadIdx.x < off) red[threadIdx.x] += red[threadIdx.x + off];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        const float nrm = (float)sqrt(red[0]);
+        if (a.out_norm != nullptr) *a.out_norm = nrm;
+        *scale_out = a.eta * sqrtf((float)a.CoK) / fmaxf(nrm, 1e-12f);
+    }
+}
+
+__global__ void __launch_bounds__(FIN_THREADS) adder_gw_scale_kernel(float* gw, int n, const float* scale) {
+    const float sc = *scale;
     const int i = blockIdx.x * FIN_THREADS + threadIdx.x;
-    if (i < a.CoK && a.eta > 0.f) a.gw[i] *= scale_s;
+    if (i < n) gw[i] *= sc;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -262,45 +287,49 @@ static GwPlan plan_gw_t(const Geom& g, const TileHint& hint) {
     a.PL = pl2;
     p.threads = round_up(a.CGO * a.CGC * a.PL, 32);
     if (p.threads > 256) { p.status = ADDER_ERR_INTERNAL; return p; }
-    // pixel tile: aim at a few segments per pixel lane
+    // pixel tile: aim at a few segments per pixel lane, shrinking until both stages fit in shared memory
+    const int budget_bytes = (hint.smem_kb > 0 ? hint.smem_kb : 100) * 1024;
+    const int spr_full = ceil_div(g.Wo, RW);
     int segs_target = a.PL * 4;
     if (segs_target < 16) segs_target = 16;
-    const int spr_full = ceil_div(g.Wo, RW);
-    a.SPR = spr_full <= segs_target ? spr_full : segs_target;
-    int rows_target = segs_target / a.SPR;
-    if (rows_target < 1) rows_target = 1;
-    if (hint.th > 0) {
-        a.TH = hint.th < g.Ho ? hint.th : g.Ho;
-    } else {
-        const int d = largest_divisor_le(g.Ho, rows_target);
-        a.TH = (2 * d > rows_target || d == g.Ho) ? d : (rows_target < g.Ho ? rows_target : g.Ho);
-    }
-    a.TI = 1;
-    if (a.TH == g.Ho) {
-        a.TI = rows_target / a.TH;
-        if (a.TI < 1) a.TI = 1;
-        if (a.TI > g.N) a.TI = g.N;
-        if (a.TI < 1) a.TI = 1;
-    }
-    if (hint.ti > 0) a.TI = hint.ti;
-    a.SEGS = a.TI * a.TH * a.SPR;
     PatchDims& px = a.pdx;
-    px.CH = a.TCI; px.TI = a.TI;
-    px.ROWS = (a.TH - 1) * S + KS;
-    px.COLS = (a.SPR * RW - 1) * S + KS;
-    px.PITCH = (KS == 1 && S == 1) ? round_up(px.COLS, 4) : (px.COLS | 1);
-    px.ROWS_PITCH = px.ROWS * px.PITCH;
-    a.XCH_STRIDE = a.TI * px.ROWS_PITCH;
     PatchDims& pg = a.pdg;
-    pg.CH = a.TM; pg.TI = a.TI;
-    pg.ROWS = a.TH;
-    pg.COLS = a.SPR * RW;
-    pg.PITCH = round_up(pg.COLS, 4) + 4;
-    pg.ROWS_PITCH = pg.ROWS * pg.PITCH;
-    a.GCH_STRIDE = a.TI * pg.ROWS_PITCH;
-    a.xs_stage = round_up(a.TCI * a.XCH_STRIDE, 4);
-    a.gs_stage = round_up(a.TM * a.GCH_STRIDE, 4);
-    p.smem = (size_t)2 * (a.xs_stage + a.gs_stage) * sizeof(float);
+    for (;; segs_target = segs_target / 2) {
+        if (segs_target < 1) segs_target = 1;
+        a.SPR = spr_full <= segs_target ? spr_full : segs_target;
+        int rows_target = segs_target / a.SPR;
+        if (rows_target < 1) rows_target = 1;
+        if (hint.th > 0) {
+            a.TH = hint.th < g.Ho ? hint.th : g.Ho;
+        } else {
+            const int d = largest_divisor_le(g.Ho, rows_target);
+            a.TH = (2 * d > rows_target || d == g.Ho) ? d : (rows_target < g.Ho ? rows_target : g.Ho);
+        }
+        a.TI = 1;
+        if (a.TH == g.Ho) {
+            a.TI = rows_target / a.TH;
+            if (a.TI > g.N) a.TI = g.N;
+            if (a.TI < 1) a.TI = 1;
+        }
+        if (hint.ti > 0) a.TI = hint.ti;
+        a.SEGS = a.TI * a.TH * a.SPR;
+        px.CH = a.TCI; px.TI = a.TI;
+        px.ROWS = (a.TH - 1) * S + KS;
+        px.COLS = (a.SPR * RW - 1) * S + KS;
+        px.PITCH = (KS == 1 && S == 1) ? round_up(px.COLS, 4) : (px.COLS | 1);
+        px.ROWS_PITCH = px.ROWS * px.PITCH;
+        a.XCH_STRIDE = a.TI * px.ROWS_PITCH;
+        pg.CH = a.TM; pg.TI = a.TI;
+        pg.ROWS = a.TH;
+        pg.COLS = a.SPR * RW;
+        pg.PITCH = round_up(pg.COLS, 4) + 4;
+        pg.ROWS_PITCH = pg.ROWS * pg.PITCH;
+        a.GCH_STRIDE = a.TI * pg.ROWS_PITCH;
+        a.xs_stage = round_up(a.TCI * a.XCH_STRIDE, 4);
+        a.gs_stage = round_up(a.TM * a.GCH_STRIDE, 4);
+        p.smem = (size_t)2 * (a.xs_stage + a.gs_stage) * sizeof(float);
+        if (p.smem <= (size_t)budget_bytes || segs_target == 1) break;
+    }
     if (p.smem > 200 * 1024) { p.status = ADDER_ERR_UNSUPPORTED; return p; }
     a.tiles_h = ceil_div(g.Ho, a.TH);
     a.tiles_w = ceil_div(spr_full, a.SPR);
@@ -318,8 +347,8 @@ static GwPlan plan_gw_t(const Geom& g, const TileHint& hint) {
     if (a.tiles_per_split < 1) a.tiles_per_split = 1;
     a.splits = ceil_div(a.tiles_total, a.tiles_per_split);
     if (a.splits < 1) a.splits = 1;
-    px.d_cols = FastDiv(px.COLS); px.d_rows = FastDiv(px.ROWS); px.d_ti = FastDiv(px.TI);
-    pg.d_cols = FastDiv(pg.COLS); pg.d_rows = FastDiv(pg.ROWS); pg.d_ti = FastDiv(pg.TI);
+    px.d_cols = FastDiv(px.COLS); px.d_rows = FastDiv(px.ROWS);
+    pg.d_cols = FastDiv(pg.COLS); pg.d_rows = FastDiv(pg.ROWS);
     a.d_tiles_h = FastDiv(a.tiles_h);
     a.d_tiles_w = FastDiv(a.tiles_w);
     a.d_spr = FastDiv(a.SPR);
@@ -327,7 +356,7 @@ static GwPlan plan_gw_t(const Geom& g, const TileHint& hint) {
     a.d_pl = FastDiv(a.PL);
     a.d_cgo = FastDiv(a.CGO);
     a.d_ci_tiles = FastDiv(a.n_ci_tiles);
-    p.fin_blocks = ceil_div(g.Co * g.Ci * KS * KS, FIN_THREADS);
+    p.fin_blocks = ceil_div(g.Co * g.Ci * KS * KS, FIN_OUT);
     return p;
 }
 
@@ -344,12 +373,25 @@ static GwPlan plan_gw(const Geom& g, const TileHint& hint) {
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+int describe_gw(const Geom& g, const TileHint& hint, char* buf, size_t n) {
+    const GwPlan p = plan_gw(g, hint);
+    if (p.status == ADDER_ERR_UNSUPPORTED && !((g.k == 1 || g.k == 3) && (g.stride == 1 || g.stride == 2))) return p.status;
+    const GwArgs& a = p.a;
+    snprintf(buf, n,
+             "gw k=%d s=%d CGO=%d CGC=%d TM=%d TCI=%d PL=%d TI=%d TH=%d SPR=%d SEGS=%d xrows=%d xcols=%d xpitch=%d gpitch=%d "
+             "threads=%d smem=%zu tiles=%d splits=%d tiles_per_split=%d out_tiles=%d fin_blocks=%d status=%d",
+             g.k, g.stride, a.CGO, a.CGC, a.TM, a.TCI, a.PL, a.TI, a.TH, a.SPR, a.SEGS, a.pdx.ROWS, a.pdx.COLS, a.pdx.PITCH,
+             a.pdg.PITCH, p.threads, p.smem, a.tiles_total, a.splits, a.tiles_per_split,
+             ceil_div(g.Co, a.TM) * a.n_ci_tiles, p.fin_blocks, p.status);
+    return ADDER_OK;
+}
+
 size_t gw_workspace_bytes(const Geom& g, const TileHint& hint) {
     const GwPlan p = plan_gw(g, hint);
     if (p.status != ADDER_OK) return 0;
     const size_t CoK = (size_t)g.Co * g.Ci * g.k * g.k;
     size_t floats = align_up((size_t)p.a.splits * CoK, 64) + align_up((size_t)p.a.splits * g.Co, 64) +
-                    align_up((size_t)p.fin_blocks, 64);
+                    align_up((size_t)p.fin_blocks + 1, 64);
     return floats * sizeof(float);
 }
 
@@ -393,8 +435,13 @@ int launch_gw(const Geom& g, const float* gout, const float* x, const float* w, 
     adder_gw_reduce_kernel<<<p.fin_blocks, FIN_THREADS, 0, stream>>>(f);
     if (cudaGetLastError() != cudaSuccess) return ADDER_ERR_CUDA;
     if (eta > 0.f || out_norm != nullptr) {
-        adder_gw_scale_kernel<<<p.fin_blocks, FIN_THREADS, 0, stream>>>(f, p.fin_blocks);
+        float* scale = norm_part + p.fin_blocks;
+        adder_gw_norm_kernel<<<1, 1024, 0, stream>>>(f, p.fin_blocks, scale);
         if (cudaGetLastError() != cudaSuccess) return ADDER_ERR_CUDA;
+        if (eta > 0.f) {
+            adder_gw_scale_kernel<<<ceil_div((int)CoK, FIN_THREADS), FIN_THREADS, 0, stream>>>(gw, (int)CoK, scale);
+            if (cudaGetLastError() != cudaSuccess) return ADDER_ERR_CUDA;
+        }
     }
     return ADDER_OK;
 }

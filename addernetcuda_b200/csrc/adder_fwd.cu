@@ -14,6 +14,8 @@
 // the KS taps over them in registers: two FP32 instructions per |x-w| term (subtract, add-abs).
 #include "common.cuh"
 #include "kernels.h"
+#include "patch_fill.cuh"
+#include <cstdio>
 
 namespace adder {
 
@@ -52,24 +54,12 @@ __global__ void __launch_bounds__(256, 2) adder_fwd_kernel(const FwdArgs a) {
         for (int j = 0; j < RW; ++j) acc[m][j] = 0.f;
 
     const int K = a.g.Ci * KK;
-    const int HW = a.g.H * a.g.W;
     const int nchunks = ceil_div(a.g.Ci, a.CK);
-    const int x_elems = a.CK * a.TI * a.IN_ROWS * a.IN_COLS;
     const int w_elems = a.wkk_pad * a.TM;      // wkk_pad = round_up(CK*KK, 8)
 
     auto fill = [&](int chunk, int stage) {
         const int ci0 = chunk * a.CK;
-        float* xs = Xs + stage * a.xs_stage;
-        for (int e = tid; e < x_elems; e += nthreads) {
-            uint32_t rho, c, rho2, r, cil, im;
-            a.d_incols.divmod(e, rho, c);
-            a.d_inrows.divmod(rho, rho2, r);
-            a.d_ti.divmod(rho2, cil, im);
-            const int n = n0 + im, ci = ci0 + cil, hi = hi0 + (int)r, wi = wi0 + (int)c;
-            const bool ok = (n < a.g.N) & (ci < a.g.Ci) & (hi >= 0) & (hi < a.g.H) & (wi >= 0) & (wi < a.g.W);
-            const float* src = ok ? a.x + ((size_t)(n * a.g.Ci + ci) * HW + hi * a.g.W + wi) : a.x;
-            cp_async4(xs + (cil * a.TI + im) * a.ROWS_PITCH + r * a.PITCH + c, src, ok);
-        }
+        fill_patch(Xs + stage * a.xs_stage, a.x, a.pd, n0, ci0, hi0, wi0, a.g.N, a.g.Ci, a.g.H, a.g.W, tid, nthreads);
         float* wsm = Ws + stage * a.ws_stage;
         const int kbase = ci0 * KK;
         const int kk_lim = a.CK * KK;
@@ -130,7 +120,7 @@ __global__ void __launch_bounds__(256, 2) adder_fwd_kernel(const FwdArgs a) {
 
     if (!active) return;
     const int n = n0 + img, ho = ho0 + hr, wo0 = wo_t0 + ws * RW;
-    if (n >= a.g.N || ho >= a.g.Ho) return;
+    if (n >= a.g.N || ho >= a.g.Ho || wo0 >= a.g.Wo) return;
     const int HoWo = a.g.Ho * a.g.Wo;
 #pragma unroll
     for (int m = 0; m < RM; ++m) {
@@ -181,11 +171,19 @@ static int pick_pitch(int cols, int segs, int spr, int th, int in_rows, int seg_
     return best;
 }
 
-template <int KS, int S, int RW, int RM>
-static int launch_fwd_t(const Geom& g, const float* x, const float* w, float* out, const TileHint& hint,
-                        cudaStream_t stream) {
+struct FwdPlan {
     FwdArgs a;
-    a.g = g; a.x = x; a.w = w; a.out = out;
+    int threads, status, ks, s, rw, rm;
+    size_t smem;
+    long long gx;
+    int gy;
+};
+
+template <int KS, int S, int RW, int RM>
+static int plan_fwd_t(const Geom& g, const float* out, const TileHint& hint, FwdPlan& p) {
+    FwdArgs& a = p.a;
+    p.ks = KS; p.s = S; p.rw = RW; p.rm = RM;
+    a.g = g;
     const int cg_max = hint.cg > 0 ? hint.cg : 8;
     a.CG = ceil_div(g.Co, RM) < cg_max ? ceil_div(g.Co, RM) : cg_max;
     a.TM = a.CG * RM;
@@ -212,12 +210,15 @@ static int launch_fwd_t(const Geom& g, const float* x, const float* w, float* ou
     }
     if (hint.ti > 0) a.TI = hint.ti;
     a.SEGS = a.TI * a.TH * a.SPR;
-    int threads = round_up(a.CG * a.SEGS, 32);
+    const int threads = round_up(a.CG * a.SEGS, 32);
+    p.threads = threads;
     if (threads > 256) return ADDER_ERR_INTERNAL;
     a.IN_ROWS = (a.TH - 1) * S + KS;
     a.IN_COLS = (a.SPR * RW - 1) * S + KS;
     a.PITCH = pick_pitch(a.IN_COLS, a.SEGS, a.SPR, a.TH, a.IN_ROWS, RW * S, S);
     a.ROWS_PITCH = a.IN_ROWS * a.PITCH;
+    a.pd.TI = a.TI; a.pd.ROWS = a.IN_ROWS; a.pd.COLS = a.IN_COLS; a.pd.PITCH = a.PITCH; a.pd.ROWS_PITCH = a.ROWS_PITCH;
+    a.pd.d_cols = FastDiv(a.IN_COLS); a.pd.d_rows = FastDiv(a.IN_ROWS);
     a.CH_STRIDE = a.TI * a.ROWS_PITCH;
     // channel chunk: fill the shared-memory budget (two CTAs per SM) without exceeding Ci
     const int budget_floats = (hint.smem_kb > 0 ? hint.smem_kb : 100) * 1024 / 4;
@@ -229,10 +230,12 @@ static int launch_fwd_t(const Geom& g, const float* x, const float* w, float* ou
         --ck;
     }
     a.CK = ck;
+    a.pd.CH = ck;
     a.wkk_pad = round_up(a.CK * KS * KS, 8);
     a.xs_stage = round_up(a.CK * a.CH_STRIDE, 4);
     a.ws_stage = a.wkk_pad * a.TMP;
     const size_t smem = (size_t)2 * (a.xs_stage + a.ws_stage) * sizeof(float);
+    p.smem = smem;
     if (smem > 200 * 1024) return ADDER_ERR_UNSUPPORTED;
     a.tiles_h = ceil_div(g.Ho, a.TH);
     a.tiles_w = ceil_div(spr_full, a.SPR);
@@ -242,19 +245,48 @@ static int launch_fwd_t(const Geom& g, const float* x, const float* w, float* ou
     a.d_segs = FastDiv(a.SEGS);
     a.d_spr = FastDiv(a.SPR);
     a.d_th = FastDiv(a.TH);
-    a.d_incols = FastDiv(a.IN_COLS);
-    a.d_inrows = FastDiv(a.IN_ROWS);
-    a.d_ti = FastDiv(a.TI);
     a.d_tm = FastDiv(a.TM);
     a.vec_store = (RW % 4 == 0) && (g.Wo % RW == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
     const long long gx = (long long)tiles_n * a.tiles_h * a.tiles_w;
     const int gy = ceil_div(g.Co, a.TM);
+    p.gx = gx; p.gy = gy;
     if (gx > 2147483647LL || gy > 65535) return ADDER_ERR_UNSUPPORTED;
+    return ADDER_OK;
+}
+
+template <int KS, int S, int RW, int RM>
+static int launch_fwd_t(const Geom& g, const float* x, const float* w, float* out, const TileHint& hint,
+                        cudaStream_t stream) {
+    FwdPlan p;
+    const int st = plan_fwd_t<KS, S, RW, RM>(g, out, hint, p);
+    if (st != ADDER_OK) return st;
+    p.a.x = x; p.a.w = w; p.a.out = out;
     auto kern = adder_fwd_kernel<KS, S, RW, RM>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
     if (e != cudaSuccess) return ADDER_ERR_CUDA;
-    kern<<<dim3((unsigned)gx, (unsigned)gy), threads, smem, stream>>>(a);
+    kern<<<dim3((unsigned)p.gx, (unsigned)p.gy), p.threads, p.smem, stream>>>(p.a);
     return cudaGetLastError() == cudaSuccess ? ADDER_OK : ADDER_ERR_CUDA;
+}
+
+int describe_fwd(const Geom& g, const TileHint& hint, char* buf, size_t n) {
+    const bool rw7 = (g.Wo % 8 != 0) && (g.Wo % 7 == 0);
+    FwdPlan p;
+    int st = ADDER_ERR_UNSUPPORTED;
+#define ADDER_FWD_PLAN(KS_, S_)                                                                  \
+    if (g.k == KS_ && g.stride == S_)                                                            \
+        st = rw7 ? plan_fwd_t<KS_, S_, 7, 8>(g, nullptr, hint, p) : plan_fwd_t<KS_, S_, 8, 8>(g, nullptr, hint, p);
+    ADDER_FWD_PLAN(3, 1)
+    ADDER_FWD_PLAN(3, 2)
+    ADDER_FWD_PLAN(1, 1)
+    ADDER_FWD_PLAN(1, 2)
+#undef ADDER_FWD_PLAN
+    if (st == ADDER_ERR_UNSUPPORTED && !((g.k == 1 || g.k == 3) && (g.stride == 1 || g.stride == 2))) return st;
+    snprintf(buf, n,
+             "fwd k=%d s=%d RW=%d RM=%d CG=%d TM=%d TI=%d TH=%d SPR=%d SEGS=%d CK=%d rows=%d cols=%d pitch=%d "
+             "threads=%d smem=%zu grid=(%lld,%d) status=%d",
+             p.ks, p.s, p.rw, p.rm, p.a.CG, p.a.TM, p.a.TI, p.a.TH, p.a.SPR, p.a.SEGS, p.a.CK, p.a.IN_ROWS, p.a.IN_COLS,
+             p.a.PITCH, p.threads, p.smem, p.gx, p.gy, st);
+    return ADDER_OK;
 }
 
 int launch_fwd(const Geom& g, const float* x, const float* w, float* out, const TileHint& hint,

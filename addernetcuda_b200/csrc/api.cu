@@ -165,6 +165,19 @@ int adder_b200_backward_col(const float* grad_y, const float* x, const float* w,
     return adder_b200_conv_weight_col(grad_y, x, w, grad_w, K, P, Co, workspace, workspace_bytes, stream);
 }
 
+int adder_b200_describe_plan(int op, int n, int ci, int h, int wd, int co, int k, int stride, int pad, int flags,
+                             char* buf, size_t buf_bytes) {
+    if (buf == nullptr || buf_bytes == 0) return ADDER_ERR_NULL_POINTER;
+    Geom g;
+    const int st = make_geom(n, ci, h, wd, co, k, stride, pad, &g);
+    if (st != ADDER_OK) return st;
+    buf[0] = 0;
+    if (op == 0) return describe_fwd(g, g_hints[0].load(), buf, buf_bytes);
+    if (op == 1) return describe_gx(g, (flags & ADDER_FLAG_FAST_CLAMP) != 0, g_hints[1].load(), buf, buf_bytes);
+    if (op == 2) return describe_gw(g, g_hints[2].load(), buf, buf_bytes);
+    return ADDER_ERR_BAD_SHAPE;
+}
+
 int adder_b200_set_tile_hint(int op, int threads, int channel_groups, int tile_rows, int tile_images,
                              int chunk_channels, int smem_kb) {
     if (op < 0 || op > 2) return ADDER_ERR_BAD_SHAPE;

@@ -26,7 +26,8 @@ struct FwdArgs {
     int TI, TH, SPR, SEGS, CG, TM, TMP, CK;
     int IN_ROWS, IN_COLS, PITCH, ROWS_PITCH, CH_STRIDE;
     int xs_stage, ws_stage, wkk_pad, tiles_h, tiles_w, vec_store;
-    FastDiv d_tiles_h, d_tiles_w, d_segs, d_spr, d_th, d_incols, d_inrows, d_ti, d_tm;
+    PatchDims pd;        // haloed input patch staged per input-channel chunk
+    FastDiv d_tiles_h, d_tiles_w, d_segs, d_spr, d_th, d_tm;
 };
 
 struct GxArgs {
@@ -75,5 +76,9 @@ size_t gw_workspace_bytes(const Geom& g, const TileHint& hint);
 int launch_gw(const Geom& g, const float* gout, const float* x, const float* w, float* gw, float eta,
               float* out_norm, int accumulate, void* workspace, size_t workspace_bytes, const TileHint& hint,
               cudaStream_t s);
+
+int describe_fwd(const Geom& g, const TileHint& hint, char* buf, size_t n);
+int describe_gx(const Geom& g, int fast, const TileHint& hint, char* buf, size_t n);
+int describe_gw(const Geom& g, const TileHint& hint, char* buf, size_t n);
 
 }  // namespace adder

@@ -8,23 +8,31 @@ namespace adder {
 
 struct PatchDims {
     int CH, TI, ROWS, COLS, PITCH, ROWS_PITCH;   // patch extents and shared-memory pitches
-    FastDiv d_cols, d_rows, d_ti;
+    FastDiv d_cols, d_rows;
 };
 
 __device__ __forceinline__ void fill_patch(float* dst, const float* __restrict__ src, const PatchDims& p,
                                            int n0, int c0, int row0, int col0, int N, int C, int Hs, int Ws,
                                            int tid, int nthreads) {
-    const int elems = p.CH * p.TI * p.ROWS * p.COLS;
+    // The (image, row, column) decoding and the bounds test are done once per patch position and
+    // reused for every channel of the chunk; per channel only two adds and the copy remain.
+    const int plane_elems = p.TI * p.ROWS * p.COLS;
     const int plane = Hs * Ws;
-    for (int e = tid; e < elems; e += nthreads) {
-        uint32_t rho, q, rho2, r, c, i;
+    const int ch_stride = p.TI * p.ROWS_PITCH;
+    const int nch = C - c0 < p.CH ? C - c0 : p.CH;      // channels past the tensor's end are zero-filled
+    for (int e = tid; e < plane_elems; e += nthreads) {
+        uint32_t rho, q, i, r;
         p.d_cols.divmod(e, rho, q);
-        p.d_rows.divmod(rho, rho2, r);
-        p.d_ti.divmod(rho2, c, i);
-        const int n = n0 + (int)i, ch = c0 + (int)c, row = row0 + (int)r, col = col0 + (int)q;
-        const bool ok = (n < N) & (ch < C) & (row >= 0) & (row < Hs) & (col >= 0) & (col < Ws);
-        const float* s = ok ? src + ((size_t)(n * C + ch) * plane + row * Ws + col) : src;
-        cp_async4(dst + (c * p.TI + i) * p.ROWS_PITCH + r * p.PITCH + q, s, ok);
+        p.d_rows.divmod(rho, i, r);
+        const int n = n0 + (int)i, row = row0 + (int)r, col = col0 + (int)q;
+        const bool ok = (n < N) & (row >= 0) & (row < Hs) & (col >= 0) & (col < Ws);
+        const float* s = ok ? src + ((size_t)(n * C + c0) * plane + row * Ws + col) : src;
+        float* d = dst + i * p.ROWS_PITCH + r * p.PITCH + q;
+#pragma unroll 4
+        for (int c = 0; c < p.CH; ++c) {
+            const bool okc = ok & (c < nch);
+            cp_async4(d + c * ch_stride, okc ? s + (size_t)c * plane : src, okc);
+        }
     }
 }
 

@@ -131,6 +131,12 @@ ADDER_API int adder_b200_backward_col(const float* grad_y, const float* x, const
 ADDER_API int adder_b200_set_tile_hint(int op, int threads, int channel_groups, int tile_rows, int tile_images,
                              int chunk_channels, int smem_kb);
 
+/* Writes a one-line description of the tile plan the library would use for this layer on the
+ * current device (op: 0 forward, 1 input gradient, 2 weight gradient) into buf (NUL-terminated,
+ * truncated to buf_bytes).  Launches nothing; works without a GPU.  No reference counterpart. */
+ADDER_API int adder_b200_describe_plan(int op, int n, int ci, int h, int wd, int co, int k, int stride, int pad,
+                                       int flags, char* buf, size_t buf_bytes);
+
 #ifdef __cplusplus
 }
 #endif

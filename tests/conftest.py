@@ -29,6 +29,19 @@ class Golden:
         p = f"{case}/{key}"
         return self.z[p + ".idx"], self.z[p + ".val"], float(self.z[p + ".sum"]), float(self.z[p + ".sumsq"])
 
+    def pair(self, case, key, got):
+        """(got restricted to the stored positions, stored reference values) as float64 torch tensors."""
+        import torch
+        if isinstance(got, torch.Tensor):
+            got = got.detach().cpu().numpy()
+        flat = np.asarray(got, dtype=np.float64).reshape(-1)
+        if self.has_full(case, key):
+            want = self.full(case, key).astype(np.float64).reshape(-1)
+            assert want.size == flat.size, f"{case}/{key}: {flat.size} values vs {want.size}"
+            return torch.from_numpy(flat), torch.from_numpy(want)
+        idx, val, _, _ = self.sample(case, key)
+        return torch.from_numpy(flat[idx]), torch.from_numpy(val.astype(np.float64))
+
     def check(self, case, key, got, rel=1e-5, abs_=1e-4):
         """Compare `got` (numpy or torch, any device) with the stored reference output.
         Returns (ok, max_abs_err, message)."""
