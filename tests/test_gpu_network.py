@@ -42,16 +42,78 @@ def test_resnet20_step_matches_reference(batch, fast_clamp):
     print("   ", msg)
     assert ok, msg
     assert abs(float(loss.detach()) - float(z["loss"])) <= 1e-4 + 1e-5 * abs(float(z["loss"]))
-    worst_name, worst_err, failures = None, 0.0, []
+    # Gradients: |got - want| <= 1e-4 + 1e-5*|want|, widened for a tensor only where the reference does
+    # not reproduce ITSELF that closely: `noise/<name>` in the fixture is how far the reference's own
+    # gradient moves between fp32 and fp64 and under a 1e-6 relative perturbation of the images (a few
+    # weight gradients of the last stage are tiny sums of large terms; one ReLU gate flipping upstream
+    # moves them by 1e-3 after the norm rescale).  The layer-level tests pin those layers exactly.
+    worst_name, worst_err, failures, widened = None, 0.0, [], []
     for k, p in net.named_parameters():
-        ok, err, msg = O.compare(k, p.grad, torch.from_numpy(z["grad/" + k]))
+        want = torch.from_numpy(z["grad/" + k])
+        noise = float(z["noise/" + k])
+        ok, err, msg = O.compare(k, p.grad, want)
         if err > worst_err:
             worst_name, worst_err = k, err
         if not ok:
-            failures.append(msg)
+            ok2, _, msg2 = O.compare(k, p.grad, want, abs_=1e-4 + 5.0 * noise)
+            if ok2:
+                widened.append(f"{k}: err {err:.2e}, reference self-noise {noise:.2e}")
+            else:
+                failures.append(msg2 + f" (reference self-noise {noise:.2e})")
     print(f"    worst gradient tensor: {worst_name} max_abs_err={worst_err:.3e} "
-          f"({len(list(net.parameters()))} tensors compared)")
+          f"({len(list(net.parameters()))} tensors compared; {len(widened)} judged against reference self-noise)")
+    for wmsg in widened:
+        print("      ", wmsg)
     assert not failures, "\n".join(failures)
+    assert len(widened) <= 3, widened
+
+
+def test_adder_layers_inside_the_network_match_oracle_on_their_own_inputs():
+    """During a batch-256 ResNet-20 step every adder layer's (x, w, grad_out) is recorded; a set of
+    layers covering every shape class, including the ill-conditioned last-stage ones, is then checked
+    against the float64 oracle evaluated on exactly those tensors."""
+    from addernetcuda_b200 import adder as A, adder_cuda as ac
+    net = _build()
+    images, labels = resnet20_batch(256, SEED)
+    images, labels = torch.from_numpy(images).to(DEV), torch.from_numpy(labels).to(DEV)
+    net.train()
+    rec = []
+    orig_bw = ac.backward_weight
+
+    def rec_bw(grad_out, x, w, stride=1, padding=0, eta=ac.ETA, out=None, return_norm=False):
+        r = orig_bw(grad_out, x, w, stride, padding, eta, out, return_norm)
+        rec.append(dict(g=grad_out, x=x, w=w, s=stride, p=padding, gw=r.clone()))
+        return r
+
+    ac.backward_weight = rec_bw
+    try:
+        logits = net(images)
+        torch.nn.functional.cross_entropy(logits, labels).backward()
+    finally:
+        ac.backward_weight = orig_bw
+    torch.cuda.synchronize()
+    assert len(rec) == 20
+    # backward order: last layer first.  pick by weight shape: one of each class + both conv1 of stage 3
+    seen, picked = {}, []
+    for i, r in enumerate(rec):
+        key = (tuple(r["w"].shape), r["s"])
+        seen[key] = seen.get(key, 0) + 1
+        if seen[key] == 1 or (key == ((64, 64, 3, 3), 1) and seen[key] in (2, 4)):
+            picked.append(i)
+    assert len(picked) >= 8
+    for i in picked:
+        r = rec[i]
+        g, x, w = r["g"].cpu(), r["x"].cpu(), r["w"].cpu()
+        want_gx, want_gws, _ = O.adder2d_backward_direct(g, x, w, r["s"], r["p"])
+        want_out = O.adder2d_forward_direct(x[:8], w, r["s"], r["p"])
+        name = f"layer#{i} w{tuple(w.shape)} s{r['s']}"
+        for what, got, want in ((name + " grad_w", r["gw"], want_gws),
+                                (name + " grad_x", ac.backward_input(r["g"], r["x"], r["w"], r["s"], r["p"]), want_gx),
+                                (name + " grad_x(fast)", ac.backward_input(r["g"], r["x"], r["w"], r["s"], r["p"], True), want_gx),
+                                (name + " out[:8]", ac.forward(r["x"][:8].contiguous(), r["w"], r["s"], r["p"]), want_out)):
+            ok, err, msg = O.compare(what, got, want)
+            print("   ", msg)
+            assert ok, msg
 
 
 def test_graph_captured_step_equals_eager_step():
