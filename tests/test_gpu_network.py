@@ -133,7 +133,8 @@ def test_graph_captured_step_equals_eager_step():
             ts.warmup(1)
             ts.capture()
             net.load_state_dict(state)
-            ts.opt.state.clear()
+            for st in ts.opt.state.values():          # the graph keeps using these buffers: reset in place
+                st["momentum_buffer"].zero_()
         losses = [float(ts.run()) for _ in range(2)]
         torch.cuda.synchronize()
         results.append((losses, {k: v.clone() for k, v in net.state_dict().items()}))
