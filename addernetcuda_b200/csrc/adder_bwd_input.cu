@@ -143,8 +143,7 @@ __global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
                     for (int kh = 0; kh < KS; ++kh) {
                         const float* gr = gcol + ((int)hr + KS - 1 - kh) * a.pd.PITCH;
                         float gv[RW + KS - 1];
-#pragma unroll
-                        for (int i = 0; i < RW + KS - 1; ++i) gv[i] = gr[i];
+                        load_run<RW + KS - 1, (RW % 4 == 0)>(gv, gr);
 #pragma unroll
                         for (int kw = 0; kw < KS; ++kw) {
                             const float4 t = *reinterpret_cast<const float4*>(wch + (kh * KS + kw) * a.TCIP);
@@ -285,7 +284,7 @@ static int plan_gx_t(const Geom& g, const TileHint& hint, GxPlan& p) {
     a.CGI = ceil_div(g.Ci, RC) < cg_max ? ceil_div(g.Ci, RC) : cg_max;
     a.TCI = a.CGI * RC;
     a.TCIP = a.TCI + 4;
-    const int threads_target = hint.threads > 0 ? hint.threads : 256;
+    const int threads_target = hint.threads > 0 ? hint.threads : 128;
     int segs_target = threads_target / a.CGI;
     if (segs_target < 1) segs_target = 1;
     const int class_px = ceil_div(g.W, S);                 // pixels of one column parity in a row
@@ -319,7 +318,14 @@ static int plan_gx_t(const Geom& g, const TileHint& hint, GxPlan& p) {
     pd.TI = a.TI;
     pd.ROWS = (S == 1) ? a.TH + KS - 1 : (a.TH + KS - 2) / S + 2;
     pd.COLS = a.SPRC * RW + (S - 1 + g.pad) / S - floor_div(g.pad - (KS - 1), S);
-    pd.PITCH = pick_pitch_gx(pd.COLS, a.SEGS, a.SPR, a.SPRC, a.TH, pd.ROWS, RW);
+    if (S == 1 && RW % 4 == 0) {
+        const int spr = a.SPR, th = a.TH, rows = pd.ROWS, segs = a.SEGS;
+        pd.PITCH = pick_pitch_vec(pd.COLS, segs < 32 ? segs : 32, [=](int l, int& row, int& col) {
+            const int ws = l % spr, t2 = l / spr;
+            row = (t2 / th) * rows + (t2 % th); col = ws * RW; });
+    } else {
+        pd.PITCH = pick_pitch_gx(pd.COLS, a.SEGS, a.SPR, a.SPRC, a.TH, pd.ROWS, RW);
+    }
     pd.ROWS_PITCH = pd.ROWS * pd.PITCH;
     a.CH_STRIDE = a.TI * pd.ROWS_PITCH;
     a.g1_size = FAST ? a.CH_STRIDE : 0;
@@ -369,20 +375,33 @@ static int launch_gx_t(const Geom& g, const float* gout, const float* x, const f
     return cudaGetLastError() == cudaSuccess ? ADDER_OK : ADDER_ERR_CUDA;
 }
 
-int describe_gx(const Geom& g, int fast, const TileHint& hint, char* buf, size_t n) {
+// Register tile: 4 input channels x RW pixels.  8-pixel segments unless the layer is too small to fill
+// the GPU with them (see choose_fwd_tile); 7-pixel segments for 7/14/28-wide planes.
+static int choose_gx_rw(const Geom& g, const TileHint& hint) {
+    if (hint.rw > 0) return hint.rw;
     const int class_px = ceil_div(g.W, g.stride);
-    const bool rw7 = (class_px % 8 != 0) && (class_px % 7 == 0);
+    if ((class_px % 8 != 0) && (class_px % 7 == 0)) return 7;
+    if (class_px % 4 != 0) return 8;
+    const long long threads8 = (long long)g.N * g.H * g.stride * ceil_div(class_px, 8) * ceil_div(g.Ci, 4);
+    return (threads8 >= 75000 || class_px % 8 != 0 && false) ? 8 : 4;
+}
+
+#define ADDER_GX_DISPATCH(CALL)                                                             \
+    if (g.k == 3 && g.stride == 1) { ADDER_GX_TILES(3, 1, CALL) }                           \
+    else if (g.k == 3 && g.stride == 2) { ADDER_GX_TILES(3, 2, CALL) }                      \
+    else if (g.k == 1 && g.stride == 1) { ADDER_GX_TILES(1, 1, CALL) }                      \
+    else if (g.k == 1 && g.stride == 2) { ADDER_GX_TILES(1, 2, CALL) }
+#define ADDER_GX_TILES(KS_, S_, CALL)                                                       \
+    if (rw == 7) { if (fast) { CALL(KS_, S_, 7, 4, true) } else { CALL(KS_, S_, 7, 4, false) } }        \
+    else if (rw == 4) { if (fast) { CALL(KS_, S_, 4, 4, true) } else { CALL(KS_, S_, 4, 4, false) } }   \
+    else { if (fast) { CALL(KS_, S_, 8, 4, true) } else { CALL(KS_, S_, 8, 4, false) } }
+
+int describe_gx(const Geom& g, int fast, const TileHint& hint, char* buf, size_t n) {
+    const int rw = choose_gx_rw(g, hint);
     GxPlan p;
     int st = ADDER_ERR_UNSUPPORTED;
-#define ADDER_GX_PLAN(KS_, S_)                                                                          \
-    if (g.k == KS_ && g.stride == S_) {                                                                 \
-        if (fast) st = rw7 ? plan_gx_t<KS_, S_, 7, 4, true>(g, hint, p) : plan_gx_t<KS_, S_, 8, 4, true>(g, hint, p); \
-        else st = rw7 ? plan_gx_t<KS_, S_, 7, 4, false>(g, hint, p) : plan_gx_t<KS_, S_, 8, 4, false>(g, hint, p);    \
-    }
-    ADDER_GX_PLAN(3, 1)
-    ADDER_GX_PLAN(3, 2)
-    ADDER_GX_PLAN(1, 1)
-    ADDER_GX_PLAN(1, 2)
+#define ADDER_GX_PLAN(KS_, S_, RW_, RC_, FAST_) st = plan_gx_t<KS_, S_, RW_, RC_, FAST_>(g, hint, p);
+    ADDER_GX_DISPATCH(ADDER_GX_PLAN)
 #undef ADDER_GX_PLAN
     if (st == ADDER_ERR_UNSUPPORTED && !((g.k == 1 || g.k == 3) && (g.stride == 1 || g.stride == 2))) return st;
     snprintf(buf, n,
@@ -395,21 +414,11 @@ int describe_gx(const Geom& g, int fast, const TileHint& hint, char* buf, size_t
 
 int launch_gx(const Geom& g, const float* gout, const float* x, const float* w, float* gx, int fast,
               int accumulate, const TileHint& hint, cudaStream_t stream) {
-    const int class_px = ceil_div(g.W, g.stride);
-    const bool rw7 = (class_px % 8 != 0) && (class_px % 7 == 0);
-#define ADDER_GX_CASE(KS_, S_)                                                                              \
-    if (g.k == KS_ && g.stride == S_) {                                                                     \
-        if (fast)                                                                                           \
-            return rw7 ? launch_gx_t<KS_, S_, 7, 4, true>(g, gout, x, w, gx, accumulate, hint, stream)       \
-                       : launch_gx_t<KS_, S_, 8, 4, true>(g, gout, x, w, gx, accumulate, hint, stream);      \
-        return rw7 ? launch_gx_t<KS_, S_, 7, 4, false>(g, gout, x, w, gx, accumulate, hint, stream)          \
-                   : launch_gx_t<KS_, S_, 8, 4, false>(g, gout, x, w, gx, accumulate, hint, stream);         \
-    }
-    ADDER_GX_CASE(3, 1)
-    ADDER_GX_CASE(3, 2)
-    ADDER_GX_CASE(1, 1)
-    ADDER_GX_CASE(1, 2)
-#undef ADDER_GX_CASE
+    const int rw = choose_gx_rw(g, hint);
+#define ADDER_GX_LAUNCH(KS_, S_, RW_, RC_, FAST_) \
+    return launch_gx_t<KS_, S_, RW_, RC_, FAST_>(g, gout, x, w, gx, accumulate, hint, stream);
+    ADDER_GX_DISPATCH(ADDER_GX_LAUNCH)
+#undef ADDER_GX_LAUNCH
     return ADDER_ERR_UNSUPPORTED;
 }
 

@@ -28,9 +28,11 @@ template <int KS, int S, int RW, int RM, int RC>
 __global__ void __launch_bounds__(256, 2) adder_gw_kernel(const GwArgs a) {
     constexpr int KK = KS * KS;
     constexpr int XW = (RW - 1) * S + KS;
+    constexpr bool VEC = (RW % 4 == 0);      // segment starts are 16-byte aligned in both patches
     extern __shared__ __align__(16) float smem[];
     float* const Xs = smem;
     float* const Gs = smem + 2 * a.xs_stage;
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *a.ticket = 0u;   // for the finishing kernel
 
     const int tid = threadIdx.x;
     const int nthreads = blockDim.x;
@@ -124,8 +126,7 @@ __global__ void __launch_bounds__(256, 2) adder_gw_kernel(const GwArgs a) {
                     for (int kh = 0; kh < KS; ++kh) {
                         const float* xr = xp + c * a.XCH_STRIDE + kh * a.pdx.PITCH;
                         float xv[XW];
-#pragma unroll
-                        for (int i = 0; i < XW; ++i) xv[i] = xr[i];
+                        load_run<XW, VEC>(xv, xr);
 #pragma unroll
                         for (int kw = 0; kw < KS; ++kw)
 #pragma unroll
@@ -172,6 +173,7 @@ __global__ void __launch_bounds__(256, 2) adder_gw_kernel(const GwArgs a) {
 constexpr int FIN_THREADS = 256;
 constexpr int FIN_OUT = 32;                       // gradient elements per reduce block
 constexpr int FIN_LANES = FIN_THREADS / FIN_OUT;  // threads that share one element and split the slices
+constexpr int FUSED_FINISH_MAX = 1 << 17;         // gradients up to this many elements finish in one kernel
 
 // gw[i] = sum_s part[s][i] - w[i] * sum_s gsum_part[s][co(i)], plus the block's partial of sum gw^2.
 // Thread (o, lane) adds the slices lane, lane+8, ... in double precision; the 8 lanes of an element
@@ -233,6 +235,70 @@ __global__ void __launch_bounds__(1024) adder_gw_norm_kernel(const GwFinishArgs 
         const float nrm = (float)sqrt(red[0]);
         if (a.out_norm != nullptr) *a.out_norm = nrm;
         *scale_out = a.eta * sqrtf((float)a.CoK) / fmaxf(nrm, 1e-12f);
+    }
+}
+
+// Small gradients: one kernel does all three finishing steps.  Every block reduces its 32 elements
+// and publishes its partial sum of squares; the block that draws the last ticket adds the partials
+// in index order (so the result does not depend on which block that is), derives the scale and
+// applies it to the whole gradient.  The ticket counter is zeroed by the main kernel of the same call.
+__global__ void __launch_bounds__(FIN_THREADS) adder_gw_finish_kernel(const GwFinishArgs a, int nblocks,
+                                                                      unsigned int* ticket) {
+    __shared__ double s_sum[FIN_LANES][FIN_OUT];
+    __shared__ double s_gs[FIN_LANES][FIN_OUT];
+    __shared__ double s_sq[FIN_THREADS];
+    __shared__ bool s_last;
+    const int o = threadIdx.x & (FIN_OUT - 1);
+    const int lane = threadIdx.x / FIN_OUT;
+    const int i = blockIdx.x * FIN_OUT + o;
+    double s = 0.0, gs = 0.0;
+    if (i < a.CoK) {
+        const int co = i / a.K;
+        const float* p = a.part + i;
+        const float* q = a.gsum_part + co;
+#pragma unroll 4
+        for (int sp = lane; sp < a.splits; sp += FIN_LANES) {
+            s += (double)p[(size_t)sp * a.CoK];
+            gs += (double)q[(size_t)sp * a.Co];
+        }
+    }
+    s_sum[lane][o] = s;
+    s_gs[lane][o] = gs;
+    __syncthreads();
+    double v2 = 0.0;
+    if (lane == 0 && i < a.CoK) {
+        double t = 0.0, g = 0.0;
+#pragma unroll
+        for (int l = 0; l < FIN_LANES; ++l) { t += s_sum[l][o]; g += s_gs[l][o]; }
+        const float vf = (float)(t - (double)a.w[i] * g);
+        if (a.accumulate) a.gw[i] += vf; else a.gw[i] = vf;
+        v2 = (double)vf * (double)vf;
+    }
+    s_sq[threadIdx.x] = (lane == 0) ? v2 : 0.0;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int k = 0; k < FIN_OUT; ++k) t += s_sq[k];
+        a.norm_part[blockIdx.x] = (float)t;
+        __threadfence();
+        s_last = (atomicAdd(ticket, 1u) == (unsigned)(nblocks - 1));
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    double t = 0.0;
+    for (int k = threadIdx.x; k < nblocks; k += FIN_THREADS) t += (double)__ldcg(a.norm_part + k);
+    s_sq[threadIdx.x] = t;
+    __syncthreads();
+    for (int off = FIN_THREADS / 2; off > 0; off >>= 1) {
+        if ((int)threadIdx.x < off) s_sq[threadIdx.x] += s_sq[threadIdx.x + off];
+        __syncthreads();
+    }
+    const float nrm = (float)sqrt(s_sq[0]);
+    if (threadIdx.x == 0 && a.out_norm != nullptr) *a.out_norm = nrm;
+    if (a.eta > 0.f) {
+        const float sc = a.eta * sqrtf((float)a.CoK) / fmaxf(nrm, 1e-12f);
+        for (int k = threadIdx.x; k < a.CoK; k += FIN_THREADS) a.gw[k] = __ldcg(a.gw + k) * sc;
     }
 }
 
@@ -316,13 +382,29 @@ static GwPlan plan_gw_t(const Geom& g, const TileHint& hint) {
         px.CH = a.TCI; px.TI = a.TI;
         px.ROWS = (a.TH - 1) * S + KS;
         px.COLS = (a.SPR * RW - 1) * S + KS;
-        px.PITCH = (KS == 1 && S == 1) ? round_up(px.COLS, 4) : (px.COLS | 1);
+        {
+            const int spr = a.SPR, th = a.TH, rows = px.ROWS, plv = a.PL;
+            if (RW % 4 == 0)
+                px.PITCH = pick_pitch_vec(px.COLS, 32, [=](int l, int& row, int& col) {
+                    const int seg = l % plv, ws = seg % spr, t2 = seg / spr;
+                    row = (t2 / th) * rows + (t2 % th) * S; col = ws * RW * S; });
+            else
+                px.PITCH = px.COLS | 1;
+        }
         px.ROWS_PITCH = px.ROWS * px.PITCH;
         a.XCH_STRIDE = a.TI * px.ROWS_PITCH;
         pg.CH = a.TM; pg.TI = a.TI;
         pg.ROWS = a.TH;
         pg.COLS = a.SPR * RW;
-        pg.PITCH = round_up(pg.COLS, 4) + 4;
+        {
+            const int spr = a.SPR, th = a.TH, plv = a.PL;
+            if (RW % 4 == 0)
+                pg.PITCH = pick_pitch_vec(pg.COLS, 32, [=](int l, int& row, int& col) {
+                    const int seg = l % plv, ws = seg % spr, t2 = seg / spr;
+                    row = (t2 / th) * th + (t2 % th); col = ws * RW; });
+            else
+                pg.PITCH = round_up(pg.COLS, 4) + 4;
+        }
         pg.ROWS_PITCH = pg.ROWS * pg.PITCH;
         a.GCH_STRIDE = a.TI * pg.ROWS_PITCH;
         a.xs_stage = round_up(a.TCI * a.XCH_STRIDE, 4);
@@ -391,7 +473,7 @@ size_t gw_workspace_bytes(const Geom& g, const TileHint& hint) {
     if (p.status != ADDER_OK) return 0;
     const size_t CoK = (size_t)g.Co * g.Ci * g.k * g.k;
     size_t floats = align_up((size_t)p.a.splits * CoK, 64) + align_up((size_t)p.a.splits * g.Co, 64) +
-                    align_up((size_t)p.fin_blocks + 1, 64);
+                    align_up((size_t)p.fin_blocks + 2, 64);
     return floats * sizeof(float);
 }
 
@@ -419,6 +501,8 @@ int launch_gw(const Geom& g, const float* gout, const float* x, const float* w, 
     p.a.part = ws;
     p.a.gsum_part = ws + align_up((size_t)p.a.splits * CoK, 64);
     float* norm_part = p.a.gsum_part + align_up((size_t)p.a.splits * g.Co, 64);
+    unsigned int* ticket = reinterpret_cast<unsigned int*>(norm_part + p.fin_blocks + 1);
+    p.a.ticket = ticket;
 
     const bool rw7 = (g.Wo % 8 != 0) && (g.Wo % 7 == 0);
     int st = ADDER_ERR_UNSUPPORTED;
@@ -432,9 +516,14 @@ int launch_gw(const Geom& g, const float* gout, const float* x, const float* w, 
     f.part = p.a.part; f.gsum_part = p.a.gsum_part; f.w = w; f.gw = gw; f.norm_part = norm_part;
     f.out_norm = out_norm; f.CoK = (int)CoK; f.K = g.Ci * g.k * g.k; f.Co = g.Co; f.splits = p.a.splits;
     f.accumulate = accumulate; f.eta = eta;
+    const bool need_norm = eta > 0.f || out_norm != nullptr;
+    if (need_norm && CoK <= (size_t)FUSED_FINISH_MAX) {
+        adder_gw_finish_kernel<<<p.fin_blocks, FIN_THREADS, 0, stream>>>(f, p.fin_blocks, ticket);
+        return cudaGetLastError() == cudaSuccess ? ADDER_OK : ADDER_ERR_CUDA;
+    }
     adder_gw_reduce_kernel<<<p.fin_blocks, FIN_THREADS, 0, stream>>>(f);
     if (cudaGetLastError() != cudaSuccess) return ADDER_ERR_CUDA;
-    if (eta > 0.f || out_norm != nullptr) {
+    if (need_norm) {
         float* scale = norm_part + p.fin_blocks;
         adder_gw_norm_kernel<<<1, 1024, 0, stream>>>(f, p.fin_blocks, scale);
         if (cudaGetLastError() != cudaSuccess) return ADDER_ERR_CUDA;

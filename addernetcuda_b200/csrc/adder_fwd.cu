@@ -96,8 +96,7 @@ __global__ void __launch_bounds__(256, 2) adder_fwd_kernel(const FwdArgs a) {
                 for (int kh = 0; kh < KS; ++kh) {
                     float xv[XW];
                     const float* xr = xs + cil * a.CH_STRIDE + kh * a.PITCH;
-#pragma unroll
-                    for (int i = 0; i < XW; ++i) xv[i] = xr[i];
+                    load_run<XW, (RW % 4 == 0)>(xv, xr);
 #pragma unroll
                     for (int kw = 0; kw < KS; ++kw) {
                         const float* wr = wsm + (cil * KK + kh * KS + kw) * a.TMP;
@@ -184,11 +183,11 @@ static int plan_fwd_t(const Geom& g, const float* out, const TileHint& hint, Fwd
     FwdArgs& a = p.a;
     p.ks = KS; p.s = S; p.rw = RW; p.rm = RM;
     a.g = g;
-    const int cg_max = hint.cg > 0 ? hint.cg : 8;
+    const int cg_max = hint.cg > 0 ? hint.cg : 64 / RM;
     a.CG = ceil_div(g.Co, RM) < cg_max ? ceil_div(g.Co, RM) : cg_max;
     a.TM = a.CG * RM;
     a.TMP = a.TM + 4;
-    const int threads_target = hint.threads > 0 ? hint.threads : 256;
+    const int threads_target = hint.threads > 0 ? hint.threads : 128;
     int segs_target = threads_target / a.CG;
     if (segs_target < 1) segs_target = 1;
     const int spr_full = ceil_div(g.Wo, RW);   // segments in a full output row
@@ -215,7 +214,14 @@ static int plan_fwd_t(const Geom& g, const float* out, const TileHint& hint, Fwd
     if (threads > 256) return ADDER_ERR_INTERNAL;
     a.IN_ROWS = (a.TH - 1) * S + KS;
     a.IN_COLS = (a.SPR * RW - 1) * S + KS;
-    a.PITCH = pick_pitch(a.IN_COLS, a.SEGS, a.SPR, a.TH, a.IN_ROWS, RW * S, S);
+    if (RW % 4 == 0) {
+        const int spr = a.SPR, th = a.TH, rows = a.IN_ROWS, segs = a.SEGS;
+        a.PITCH = pick_pitch_vec(a.IN_COLS, segs < 32 ? segs : 32, [=](int l, int& row, int& col) {
+            const int ws = l % spr, t2 = l / spr;
+            row = (t2 / th) * rows + (t2 % th) * S; col = ws * RW * S; });
+    } else {
+        a.PITCH = pick_pitch(a.IN_COLS, a.SEGS, a.SPR, a.TH, a.IN_ROWS, RW * S, S);
+    }
     a.ROWS_PITCH = a.IN_ROWS * a.PITCH;
     a.pd.TI = a.TI; a.pd.ROWS = a.IN_ROWS; a.pd.COLS = a.IN_COLS; a.pd.PITCH = a.PITCH; a.pd.ROWS_PITCH = a.ROWS_PITCH;
     a.pd.d_cols = FastDiv(a.IN_COLS); a.pd.d_rows = FastDiv(a.IN_ROWS);
@@ -268,17 +274,42 @@ static int launch_fwd_t(const Geom& g, const float* x, const float* w, float* ou
     return cudaGetLastError() == cudaSuccess ? ADDER_OK : ADDER_ERR_CUDA;
 }
 
+// Register tile (pixels x channels per thread).  The widest tile has the fewest shared-memory loads
+// per |x-w| term, but a layer with few pixels and channels then has too few threads to keep 148 SMs
+// busy (64->64 on 8x8 at batch 256 would run on 512 warps), so narrower tiles are chosen until the
+// launch has about 16 warps per SM.  Planes that are 7, 14 or 28 wide use 7-pixel segments.
+static void choose_fwd_tile(const Geom& g, const TileHint& hint, int& rw, int& rm) {
+    if (hint.rw > 0 && hint.rm > 0) { rw = hint.rw; rm = hint.rm; return; }
+    if ((g.Wo % 8 != 0) && (g.Wo % 7 == 0)) { rw = 7; rm = 8; return; }
+    if (g.Wo % 4 != 0) { rw = 8; rm = 8; return; }
+    const long long want = 75000;
+    const int cand[3][2] = {{8, 8}, {8, 4}, {4, 4}};
+    for (int c = 0; c < 3; ++c) {
+        rw = cand[c][0]; rm = cand[c][1];
+        if (g.Wo % rw != 0 && rw == 8) continue;
+        const long long threads = (long long)g.N * g.Ho * ceil_div(g.Wo, rw) * ceil_div(g.Co, rm);
+        if (threads >= want) return;
+    }
+}
+
+#define ADDER_FWD_DISPATCH(CALL)                                                            \
+    if (g.k == 3 && g.stride == 1) { ADDER_FWD_TILES(3, 1, CALL) }                          \
+    else if (g.k == 3 && g.stride == 2) { ADDER_FWD_TILES(3, 2, CALL) }                     \
+    else if (g.k == 1 && g.stride == 1) { ADDER_FWD_TILES(1, 1, CALL) }                     \
+    else if (g.k == 1 && g.stride == 2) { ADDER_FWD_TILES(1, 2, CALL) }
+#define ADDER_FWD_TILES(KS_, S_, CALL)                                                      \
+    if (rw == 7) { CALL(KS_, S_, 7, 8) }                                                    \
+    else if (rw == 8 && rm == 8) { CALL(KS_, S_, 8, 8) }                                    \
+    else if (rw == 8 && rm == 4) { CALL(KS_, S_, 8, 4) }                                    \
+    else if (rw == 4 && rm == 4) { CALL(KS_, S_, 4, 4) }
+
 int describe_fwd(const Geom& g, const TileHint& hint, char* buf, size_t n) {
-    const bool rw7 = (g.Wo % 8 != 0) && (g.Wo % 7 == 0);
+    int rw = 8, rm = 8;
+    choose_fwd_tile(g, hint, rw, rm);
     FwdPlan p;
     int st = ADDER_ERR_UNSUPPORTED;
-#define ADDER_FWD_PLAN(KS_, S_)                                                                  \
-    if (g.k == KS_ && g.stride == S_)                                                            \
-        st = rw7 ? plan_fwd_t<KS_, S_, 7, 8>(g, nullptr, hint, p) : plan_fwd_t<KS_, S_, 8, 8>(g, nullptr, hint, p);
-    ADDER_FWD_PLAN(3, 1)
-    ADDER_FWD_PLAN(3, 2)
-    ADDER_FWD_PLAN(1, 1)
-    ADDER_FWD_PLAN(1, 2)
+#define ADDER_FWD_PLAN(KS_, S_, RW_, RM_) st = plan_fwd_t<KS_, S_, RW_, RM_>(g, nullptr, hint, p);
+    ADDER_FWD_DISPATCH(ADDER_FWD_PLAN)
 #undef ADDER_FWD_PLAN
     if (st == ADDER_ERR_UNSUPPORTED && !((g.k == 1 || g.k == 3) && (g.stride == 1 || g.stride == 2))) return st;
     snprintf(buf, n,
@@ -291,16 +322,11 @@ int describe_fwd(const Geom& g, const TileHint& hint, char* buf, size_t n) {
 
 int launch_fwd(const Geom& g, const float* x, const float* w, float* out, const TileHint& hint,
                cudaStream_t stream) {
-    const bool rw7 = (g.Wo % 8 != 0) && (g.Wo % 7 == 0);
-#define ADDER_FWD_CASE(KS_, S_)                                                                  \
-    if (g.k == KS_ && g.stride == S_)                                                            \
-        return rw7 ? launch_fwd_t<KS_, S_, 7, 8>(g, x, w, out, hint, stream)                     \
-                   : launch_fwd_t<KS_, S_, 8, 8>(g, x, w, out, hint, stream);
-    ADDER_FWD_CASE(3, 1)
-    ADDER_FWD_CASE(3, 2)
-    ADDER_FWD_CASE(1, 1)
-    ADDER_FWD_CASE(1, 2)
-#undef ADDER_FWD_CASE
+    int rw = 8, rm = 8;
+    choose_fwd_tile(g, hint, rw, rm);
+#define ADDER_FWD_LAUNCH(KS_, S_, RW_, RM_) return launch_fwd_t<KS_, S_, RW_, RM_>(g, x, w, out, hint, stream);
+    ADDER_FWD_DISPATCH(ADDER_FWD_LAUNCH)
+#undef ADDER_FWD_LAUNCH
     return ADDER_ERR_UNSUPPORTED;
 }
 

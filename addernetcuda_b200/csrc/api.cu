@@ -7,7 +7,7 @@ using namespace adder;
 namespace {
 
 struct HintSlot {
-    std::atomic<int> threads{0}, cg{0}, th{0}, ti{0}, ck{0}, smem_kb{0};
+    std::atomic<int> threads{0}, cg{0}, th{0}, ti{0}, ck{0}, smem_kb{0}, rw{0}, rm{0};
     TileHint load() const {
         TileHint h;
         h.threads = threads.load(std::memory_order_relaxed);
@@ -16,6 +16,8 @@ struct HintSlot {
         h.ti = ti.load(std::memory_order_relaxed);
         h.ck = ck.load(std::memory_order_relaxed);
         h.smem_kb = smem_kb.load(std::memory_order_relaxed);
+        h.rw = rw.load(std::memory_order_relaxed);
+        h.rm = rm.load(std::memory_order_relaxed);
         return h;
     }
 };
@@ -184,6 +186,13 @@ int adder_b200_set_tile_hint(int op, int threads, int channel_groups, int tile_r
     HintSlot& s = g_hints[op];
     s.threads.store(threads); s.cg.store(channel_groups); s.th.store(tile_rows); s.ti.store(tile_images);
     s.ck.store(chunk_channels); s.smem_kb.store(smem_kb);
+    return ADDER_OK;
+}
+
+int adder_b200_set_micro_tile(int op, int pixels_per_thread, int channels_per_thread) {
+    if (op < 0 || op > 2) return ADDER_ERR_BAD_SHAPE;
+    g_hints[op].rw.store(pixels_per_thread);
+    g_hints[op].rm.store(channels_per_thread);
     return ADDER_OK;
 }
 

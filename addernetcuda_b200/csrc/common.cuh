@@ -54,6 +54,52 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
+// Loads N consecutive floats from shared memory into registers.  When ALIGNED the address is a
+// multiple of 16 bytes and the run is fetched with 128-/64-bit loads (10 values = 2 x LDS.128 + 1 x
+// LDS.64 instead of 10 scalar loads); otherwise one scalar load per value.
+template <int N, bool ALIGNED>
+__device__ __forceinline__ void load_run(float (&dst)[N], const float* __restrict__ src) {
+    if (ALIGNED) {
+        int i = 0;
+#pragma unroll
+        for (; i + 4 <= N; i += 4) {
+            const float4 v = *reinterpret_cast<const float4*>(src + i);
+            dst[i] = v.x; dst[i + 1] = v.y; dst[i + 2] = v.z; dst[i + 3] = v.w;
+        }
+        if (N % 4 >= 2) {
+            const float2 v = *reinterpret_cast<const float2*>(src + (N / 4) * 4);
+            dst[(N / 4) * 4] = v.x; dst[(N / 4) * 4 + 1] = v.y;
+        }
+        if (N % 2 == 1) dst[N - 1] = src[N - 1];
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) dst[i] = src[i];
+    }
+}
+
+// Row pitch (in floats) for a shared-memory patch read with 128-bit loads by lanes whose start
+// addresses are a0[l] + row[l] * pitch: the smallest multiple of 4 >= cols (up to +32) minimising,
+// over the four quarter-warps, the worst number of lanes that fall into one 16-byte bank group.
+template <typename F>
+inline int pick_pitch_vec(int cols, int nlanes, F lane_row_and_col) {
+    int best = (cols + 3) / 4 * 4, best_cost = 1 << 30;
+    for (int pitch = (cols + 3) / 4 * 4; pitch <= (cols + 3) / 4 * 4 + 32; pitch += 4) {
+        int cost = 0;
+        for (int q0 = 0; q0 < nlanes; q0 += 8) {
+            int cnt[8] = {0}, worst = 0;
+            for (int l = q0; l < q0 + 8 && l < nlanes; ++l) {
+                int row, col;
+                lane_row_and_col(l, row, col);
+                const int grp = ((row * pitch + col) >> 2) & 7;
+                if (++cnt[grp] > worst) worst = cnt[grp];
+            }
+            cost += worst;
+        }
+        if (cost < best_cost) { best_cost = cost; best = pitch; }
+    }
+    return best;
+}
+
 __host__ __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
 __host__ __device__ __forceinline__ int round_up(int a, int b) { return ceil_div(a, b) * b; }
 // floor(a / b) for b > 0 and any sign of a.

@@ -16,6 +16,8 @@ struct TileHint {
     int ti = 0;        // tile images
     int ck = 0;        // channels per shared-memory stage
     int smem_kb = 0;   // shared-memory budget per CTA
+    int rw = 0;        // pixels per thread segment (register tile width)
+    int rm = 0;        // channels per thread (register tile height)
 };
 
 struct FwdArgs {
@@ -48,6 +50,7 @@ struct GwArgs {
     const float* x;
     float* part;         // [splits][Co*K] partial sums of x*g
     float* gsum_part;    // [splits][Co]   partial sums of g
+    unsigned int* ticket; // zeroed by the main kernel, counted up by the finishing kernel's blocks
     PatchDims pdx;       // haloed input patch [TCI][TI*IN_ROWS][PITCH]
     PatchDims pdg;       // tile of g          [TM][TI*TH][GP]
     int TI, TH, SPR, SEGS;        // pixel tile (as in the forward kernel)

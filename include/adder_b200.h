@@ -131,6 +131,10 @@ ADDER_API int adder_b200_backward_col(const float* grad_y, const float* x, const
 ADDER_API int adder_b200_set_tile_hint(int op, int threads, int channel_groups, int tile_rows, int tile_images,
                              int chunk_channels, int smem_kb);
 
+/* Overrides the per-thread register tile of one kernel family (pixels per thread segment: 4, 7 or 8;
+ * channels per thread: 4 or 8; 0,0 restores the automatic choice).  Tuning only. */
+ADDER_API int adder_b200_set_micro_tile(int op, int pixels_per_thread, int channels_per_thread);
+
 /* Writes a one-line description of the tile plan the library would use for this layer on the
  * current device (op: 0 forward, 1 input gradient, 2 weight gradient) into buf (NUL-terminated,
  * truncated to buf_bytes).  Launches nothing; works without a GPU.  No reference counterpart. */

@@ -103,6 +103,29 @@ def test_reference_extension_entry_points(case, golden, ac):
     _assert(golden.check(case["name"], "grad_X", Xr.grad))
 
 
+@pytest.mark.parametrize("tile", [(8, 8), (8, 4), (4, 4)], ids=lambda t: "px%d_ch%d" % t)
+@pytest.mark.parametrize("name", ["r20_n4_c16to16_32x32_k3s1p1", "r20_n4_c16to32_32x32_k3s2p1", "r20_n4_c32to64_16x16_k1s2p0",
+                                  "odd_n1_c6to10_3x70_k3s1p1", "odd_n2_c7to5_9x9_k1s1p0"])
+def test_every_register_tile(name, tile, golden, ac):
+    """The launcher picks the per-thread register tile from the layer size; force each one in turn so
+    that all compiled variants are checked on small cases too."""
+    from addernetcuda_b200 import _lib
+    from tests.cases import LAYER_BY_NAME
+    lib = _lib.load()
+    case = LAYER_BY_NAME[name]
+    x, w, g = (_gpu(a) for a in draw_layer(case))
+    s, p = case["stride"], case["pad"]
+    try:
+        assert lib.adder_b200_set_micro_tile(0, tile[0], tile[1]) == 0
+        assert lib.adder_b200_set_micro_tile(1, tile[0], 4) == 0
+        _assert(golden.check(name, "out", ac.forward(x, w, s, p)))
+        _assert(golden.check(name, "grad_x", ac.backward_input(g, x, w, s, p)))
+        _assert(golden.check(name, "grad_x", ac.backward_input(g, x, w, s, p, fast_clamp=True)))
+    finally:
+        lib.adder_b200_set_micro_tile(0, 0, 0)
+        lib.adder_b200_set_micro_tile(1, 0, 0)
+
+
 def test_module_autograd_and_bias(ac):
     from addernetcuda_b200 import adder as A
     from oracle import adder_unfold as U
