@@ -28,6 +28,9 @@ SIGNATURES = {
     "adder_b200_backward_weight_workspace_bytes": (c_size_t, [*_GEOM]),
     "adder_b200_backward_weight": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                                            c_size_t, *_GEOM, c_int, c_void_p]),
+    "adder_b200_static_scratch_bytes": (c_size_t, []),
+    "adder_b200_backward_weight_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, *_GEOM,
+                                                  c_void_p]),
     "adder_b200_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_size_t,
                                     *_GEOM, c_int, c_void_p]),
     "adder_b200_conv_col": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
@@ -67,7 +70,7 @@ def check(status: int, what: str) -> None:
     if status == ADDER_OK:
         return
     msg = load().adder_b200_status_string(status).decode()
-    exc = ValueError if status in (1, 2, 3, 4, 5) else RuntimeError
+    exc = ValueError if status in (1, 2, 3, 4, 5, 8) else RuntimeError
     raise exc(f"{what}: {msg} (status {status})")
 
 

@@ -59,6 +59,7 @@ const char* adder_b200_status_string(int status) {
         case ADDER_ERR_WORKSPACE: return "workspace missing or too small";
         case ADDER_ERR_CUDA: return "CUDA runtime error";
         case ADDER_ERR_INTERNAL: return "internal tile-planning error";
+        case ADDER_ERR_TOO_LARGE: return "layer needs more scratch than the fixed in-library array holds";
         default: return "unknown status";
     }
 }

@@ -45,7 +45,8 @@ enum {
     ADDER_ERR_ALIGNMENT = 4,     /* a pointer is not aligned as documented */
     ADDER_ERR_WORKSPACE = 5,     /* workspace missing or smaller than the *_workspace_bytes() answer */
     ADDER_ERR_CUDA = 6,          /* the CUDA runtime rejected a launch or an attribute */
-    ADDER_ERR_INTERNAL = 7       /* tile planner produced an impossible plan (a bug) */
+    ADDER_ERR_INTERNAL = 7,      /* tile planner produced an impossible plan (a bug) */
+    ADDER_ERR_TOO_LARGE = 8      /* the layer needs more scratch than a fixed-capacity entry point owns */
 };
 
 /* flags for the backward entry points */
@@ -93,6 +94,23 @@ ADDER_API size_t adder_b200_backward_weight_workspace_bytes(int n, int ci, int h
 ADDER_API int adder_b200_backward_weight(const float* grad_out, const float* x, const float* w, float* grad_w, float eta,
                                float* out_norm, void* workspace, size_t workspace_bytes, int n, int ci, int h,
                                int wd, int co, int k, int stride, int pad, int flags, void* stream);
+
+/* The same weight gradient for callers that may not allocate: plugin hosts whose memory manager owns
+ * the whole GPU and forbids cudaMalloc in plugins (it stalls every stream and escapes their
+ * accounting), and bindings that are only handed input and output pointers and have no allocator to
+ * ask for a workspace.  The scratch is a fixed array of ADDER_B200_STATIC_SCRATCH_BYTES inside the
+ * library (one per GPU that loads it, held until exit); the call allocates and frees nothing.
+ * A layer whose partial sums need more returns ADDER_ERR_TOO_LARGE: use the workspace-taking entry
+ * point for it.  All calls on a device share that array, so calls that can overlap on the GPU
+ * (different streams without a dependency) race: serialise them.  Nothing in the array needs
+ * clearing between calls.  The first call on each device looks up the array's device address; make
+ * it outside any stream capture.  Results are identical to adder_b200_backward_weight().
+ * This entry point has no counterpart in the reference. */
+#define ADDER_B200_STATIC_SCRATCH_BYTES (8u << 20)
+ADDER_API size_t adder_b200_static_scratch_bytes(void);
+ADDER_API int adder_b200_backward_weight_static(const float* grad_out, const float* x, const float* w, float* grad_w,
+                                                float eta, float* out_norm, int n, int ci, int h, int wd, int co,
+                                                int k, int stride, int pad, void* stream);
 
 /* Both gradients of one layer: adder.backward (adder.py:62-80) in one call. */
 ADDER_API int adder_b200_backward(const float* grad_out, const float* x, const float* w, float* grad_x, float* grad_w,
