@@ -383,8 +383,14 @@ def run_gpu_arm(args):
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
+        # Leave without tearing the communicator down: CUDA graphs that captured collectives on it are
+        # still alive, and destroying it under them can block.  Everything is flushed and every rank has
+        # passed the barrier, so a hard exit loses nothing.
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():
