@@ -22,63 +22,77 @@ def _default_conv():
     return adder2d
 
 
+def _norm_class(fused: bool):
+    if fused:
+        from .batchnorm import FusedBatchNorm2d
+        return FusedBatchNorm2d
+    return nn.BatchNorm2d
+
+
+def _bn_act(bn, y, residual=None, relu=False):
+    """relu?(bn(y) + residual?) - one fused pass when `bn` is a FusedBatchNorm2d."""
+    if hasattr(bn, "forward") and bn.__class__.__name__ == "FusedBatchNorm2d":
+        return bn(y, residual=residual, relu=relu)
+    out = bn(y)
+    if residual is not None:
+        out = out + residual
+    return torch.relu(out) if relu else out
+
+
 class BasicBlock(nn.Module):
     """conv3x3-BN-ReLU-conv3x3-BN + shortcut, ReLU (resnet20.py:12-41)."""
     expansion = 1
 
-    def __init__(self, conv, inplanes, planes, stride=1, downsample=None):
+    def __init__(self, conv, inplanes, planes, stride=1, downsample=None, norm=nn.BatchNorm2d):
         super().__init__()
         self.conv1 = conv(inplanes, planes, kernel_size=3, stride=stride, padding=1, bias=False)
-        self.bn1 = nn.BatchNorm2d(planes)
+        self.bn1 = norm(planes)
         self.relu = nn.ReLU(inplace=True)
         self.conv2 = conv(planes, planes, kernel_size=3, stride=1, padding=1, bias=False)
-        self.bn2 = nn.BatchNorm2d(planes)
+        self.bn2 = norm(planes)
         self.downsample = downsample
         self.stride = stride
 
     def forward(self, x):
-        out = self.relu(self.bn1(self.conv1(x)))
-        out = self.bn2(self.conv2(out))
+        out = _bn_act(self.bn1, self.conv1(x), relu=True)
         res = x if self.downsample is None else self.downsample(x)
-        out += res
-        return self.relu(out)
+        return _bn_act(self.bn2, self.conv2(out), residual=res, relu=True)
 
 
 class Bottleneck(nn.Module):
     """1x1-3x3(stride)-1x1(x4) bottleneck (resnet50.py:19-55)."""
     expansion = 4
 
-    def __init__(self, conv, inplanes, planes, stride=1, downsample=None):
+    def __init__(self, conv, inplanes, planes, stride=1, downsample=None, norm=nn.BatchNorm2d):
         super().__init__()
         self.conv1 = conv(inplanes, planes, kernel_size=1, stride=1, bias=False)
-        self.bn1 = nn.BatchNorm2d(planes)
+        self.bn1 = norm(planes)
         self.conv2 = conv(planes, planes, kernel_size=3, stride=stride, padding=1, bias=False)
-        self.bn2 = nn.BatchNorm2d(planes)
+        self.bn2 = norm(planes)
         self.conv3 = conv(planes, planes * 4, kernel_size=1, stride=1, bias=False)
-        self.bn3 = nn.BatchNorm2d(planes * 4)
+        self.bn3 = norm(planes * 4)
         self.relu = nn.ReLU(inplace=True)
         self.downsample = downsample
         self.stride = stride
 
     def forward(self, x):
-        out = self.relu(self.bn1(self.conv1(x)))
-        out = self.relu(self.bn2(self.conv2(out)))
-        out = self.bn3(self.conv3(out))
+        out = _bn_act(self.bn1, self.conv1(x), relu=True)
+        out = _bn_act(self.bn2, self.conv2(out), relu=True)
         res = x if self.downsample is None else self.downsample(x)
-        out += res
-        return self.relu(out)
+        return _bn_act(self.bn3, self.conv3(out), residual=res, relu=True)
 
 
 class _ResNet(nn.Module):
     def _make_layer(self, conv, block, planes, blocks, stride=1):
+        norm = self.norm
         downsample = None
         if stride != 1 or self.inplanes != planes * block.expansion:
             downsample = nn.Sequential(
                 conv(self.inplanes, planes * block.expansion, kernel_size=1, stride=stride, bias=False),
-                nn.BatchNorm2d(planes * block.expansion))
-        layers = [block(conv, self.inplanes, planes, stride, downsample)]
+                norm(planes * block.expansion))
+        layers = [block(conv, self.inplanes, planes, stride, downsample, norm)]
         self.inplanes = planes * block.expansion
-        layers += [block(conv, self.inplanes, planes) for _ in range(1, blocks)]
+        layers += [block(conv, self.inplanes, planes, norm=norm) for _ in range(1, blocks)]
         return nn.Sequential(*layers)
 
 
@@ -86,12 +100,13 @@ class ResNet20(_ResNet):
     """Stem Conv2d(3,16,3) and the 1x1 `fc` + BatchNorm head stay multiply-based; the 18 3x3 layers
     and the two stride-2 1x1 shortcuts are adder layers (resnet20.py:44-93)."""
 
-    def __init__(self, conv=None, num_classes=10):
+    def __init__(self, conv=None, num_classes=10, fused_bn=None):
         super().__init__()
+        self.norm = _norm_class(conv is None if fused_bn is None else fused_bn)
         conv = conv or _default_conv()
         self.inplanes = 16
         self.conv1 = nn.Conv2d(3, 16, kernel_size=3, stride=1, padding=1, bias=False)
-        self.bn1 = nn.BatchNorm2d(16)
+        self.bn1 = self.norm(16)
         self.relu = nn.ReLU(inplace=True)
         self.layer1 = self._make_layer(conv, BasicBlock, 16, 3)
         self.layer2 = self._make_layer(conv, BasicBlock, 32, 3, stride=2)
@@ -101,7 +116,7 @@ class ResNet20(_ResNet):
         self.bn2 = nn.BatchNorm2d(num_classes)
 
     def forward(self, x):
-        x = self.relu(self.bn1(self.conv1(x)))
+        x = _bn_act(self.bn1, self.conv1(x), relu=True)
         x = self.layer3(self.layer2(self.layer1(x)))
         x = self.bn2(self.fc(self.avgpool(x)))
         return x.view(x.size(0), -1)
@@ -111,12 +126,13 @@ class ResNet50(_ResNet):
     """Stem Conv2d(3,64,7,s2) + maxpool and the 1x1 `fc` (with bias) + BatchNorm head stay
     multiply-based; all 52 other convolutions are adder layers (resnet50.py:58-115)."""
 
-    def __init__(self, conv=None, num_classes=1000):
+    def __init__(self, conv=None, num_classes=1000, fused_bn=None):
         super().__init__()
+        self.norm = _norm_class(conv is None if fused_bn is None else fused_bn)
         conv = conv or _default_conv()
         self.inplanes = 64
         self.conv1 = nn.Conv2d(3, 64, kernel_size=7, stride=2, padding=3, bias=False)
-        self.bn1 = nn.BatchNorm2d(64)
+        self.bn1 = self.norm(64)
         self.relu = nn.ReLU(inplace=True)
         self.maxpool = nn.MaxPool2d(kernel_size=3, stride=2, padding=1)
         self.layer1 = self._make_layer(conv, Bottleneck, 64, 3)
@@ -128,7 +144,7 @@ class ResNet50(_ResNet):
         self.bn2 = nn.BatchNorm2d(num_classes)
 
     def forward(self, x):
-        x = self.maxpool(self.relu(self.bn1(self.conv1(x))))
+        x = self.maxpool(_bn_act(self.bn1, self.conv1(x), relu=True))
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
         x = self.bn2(self.fc(self.avgpool(x)))
         return x.view(x.size(0), -1)

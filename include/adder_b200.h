@@ -142,6 +142,28 @@ ADDER_API int adder_b200_conv_input_col(const float* grad_y, const float* x, con
 ADDER_API int adder_b200_backward_col(const float* grad_y, const float* x, const float* w, float* grad_w, float* grad_i,
                             int K, int P, int Co, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- the batch normalisation that follows every adder layer (training mode) ------------------
+ * The reference networks wrap each adder2d in nn.BatchNorm2d (+ReLU, + the residual add at the end
+ * of a block): resnet20.py:28-40, resnet50.py:38-53.  These entry points compute exactly that on
+ * NCHW fp32 tensors [n, c, hw]: batch statistics per channel (biased variance for normalising,
+ * unbiased for running_var, as torch.nn.BatchNorm2d), z = gamma*(y-mean)*invstd + beta
+ * [+ residual] [then ReLU].  save_mean / save_invstd [c] are outputs kept for the backward pass;
+ * running_mean / running_var [c] may both be NULL.  Workspace: 16-byte aligned scratch of
+ * adder_b200_batchnorm_workspace_bytes(); tensors must be 16-byte aligned when hw % 4 == 0. */
+ADDER_API size_t adder_b200_batchnorm_workspace_bytes(int n, int c, int hw);
+ADDER_API int adder_b200_batchnorm_forward(const float* y, const float* gamma, const float* beta,
+                                           const float* residual, float* z, float* save_mean, float* save_invstd,
+                                           float* running_mean, float* running_var, float eps, float momentum,
+                                           int relu, void* workspace, size_t workspace_bytes, int n, int c, int hw,
+                                           void* stream);
+/* Backward of the above: dz is the gradient of z; with relu != 0 it is first masked by z > 0 (z: the
+ * forward output).  Outputs: dy, dgamma[c], dbeta[c] and, when dresidual != NULL, the gradient of the
+ * residual input (= the masked dz). */
+ADDER_API int adder_b200_batchnorm_backward(const float* dz, const float* y, const float* z, const float* gamma,
+                                            const float* save_mean, const float* save_invstd, float* dy,
+                                            float* dresidual, float* dgamma, float* dbeta, int relu, void* workspace,
+                                            size_t workspace_bytes, int n, int c, int hw, void* stream);
+
 /* ---- tuning hook ---------------------------------------------------------------------------
  * Overrides the tile heuristics of one kernel family for subsequent calls from any thread
  * (op: 0 forward, 1 input gradient, 2 weight gradient; a value of 0 restores the automatic
