@@ -280,11 +280,11 @@ static int plan_gx_t(const Geom& g, const TileHint& hint, GxPlan& p) {
     GxArgs& a = p.a;
     p.ks = KS; p.s = S; p.rw = RW; p.rc = RC; p.fast = FAST;
     a.g = g;
-    const int cg_max = hint.cg > 0 ? hint.cg : 8;
+    const int threads_target = hint.threads > 0 ? hint.threads : 256;
+    const int cg_max = hint.cg > 0 ? hint.cg : 4;
     a.CGI = ceil_div(g.Ci, RC) < cg_max ? ceil_div(g.Ci, RC) : cg_max;
     a.TCI = a.CGI * RC;
     a.TCIP = a.TCI + 4;
-    const int threads_target = hint.threads > 0 ? hint.threads : 128;
     int segs_target = threads_target / a.CGI;
     if (segs_target < 1) segs_target = 1;
     const int class_px = ceil_div(g.W, S);                 // pixels of one column parity in a row
@@ -300,8 +300,10 @@ static int plan_gx_t(const Geom& g, const TileHint& hint, GxPlan& p) {
     }
     if (a.TH > g.H) a.TH = g.H;
     a.TI = 1;
+    int ti_budget = 1;   // tile images before clamping to the batch: the chunk size must not depend on N
     if (a.TH == g.H) {
         a.TI = rows_target / a.TH;
+        ti_budget = a.TI > 1 ? a.TI : 1;
         if (a.TI < 1) a.TI = 1;
         if (a.TI > g.N) a.TI = g.N;
         if (a.TI < 1) a.TI = 1;
@@ -330,10 +332,11 @@ static int plan_gx_t(const Geom& g, const TileHint& hint, GxPlan& p) {
     a.CH_STRIDE = a.TI * pd.ROWS_PITCH;
     a.g1_size = FAST ? a.CH_STRIDE : 0;
     const int budget_floats = (hint.smem_kb > 0 ? hint.smem_kb : 100) * 1024 / 4;
-    int cko = hint.ck > 0 ? hint.ck : 8;
+    int cko = hint.ck > 0 ? hint.ck : (KS == 1 ? 64 : 16);
     if (cko > g.Co) cko = g.Co;
     while (cko > 1) {
-        const int need = 2 * (round_up(cko * a.CH_STRIDE, 4) + cko * KS * KS * a.TCIP) + a.g1_size + RC * RW * threads;
+        const int need = 2 * (round_up(cko * ti_budget * pd.ROWS_PITCH, 4) + cko * KS * KS * a.TCIP) +
+                         (FAST ? ti_budget * pd.ROWS_PITCH : 0) + RC * RW * 256;
         if (need <= budget_floats) break;
         --cko;
     }
@@ -382,8 +385,7 @@ static int choose_gx_rw(const Geom& g, const TileHint& hint) {
     const int class_px = ceil_div(g.W, g.stride);
     if ((class_px % 8 != 0) && (class_px % 7 == 0)) return 7;
     if (class_px % 4 != 0) return 8;
-    const long long threads8 = (long long)g.N * g.H * g.stride * ceil_div(class_px, 8) * ceil_div(g.Ci, 4);
-    return (threads8 >= 75000 || class_px % 8 != 0 && false) ? 8 : 4;
+    return 4;      // 4-pixel segments won every sweep of the ResNet-20 layer shapes
 }
 
 #define ADDER_GX_DISPATCH(CALL)                                                             \

@@ -356,7 +356,7 @@ static GwPlan plan_gw_t(const Geom& g, const TileHint& hint) {
     // pixel tile: aim at a few segments per pixel lane, shrinking until both stages fit in shared memory
     const int budget_bytes = (hint.smem_kb > 0 ? hint.smem_kb : 100) * 1024;
     const int spr_full = ceil_div(g.Wo, RW);
-    int segs_target = a.PL * 4;
+    int segs_target = a.PL * (KS == 1 ? 16 : 4);     // a 1x1 layer has 9x less work per pixel: larger pixel tiles
     if (segs_target < 16) segs_target = 16;
     PatchDims& px = a.pdx;
     PatchDims& pg = a.pdg;

@@ -183,11 +183,12 @@ static int plan_fwd_t(const Geom& g, const float* out, const TileHint& hint, Fwd
     FwdArgs& a = p.a;
     p.ks = KS; p.s = S; p.rw = RW; p.rm = RM;
     a.g = g;
-    const int cg_max = hint.cg > 0 ? hint.cg : 64 / RM;
+    const int threads_target = hint.threads > 0 ? hint.threads : 128;
+    // few channel groups per CTA: the weight slab is re-staged by every CTA, the pixels are not
+    const int cg_max = hint.cg > 0 ? hint.cg : (threads_target / 32 > 2 ? threads_target / 32 : 2);
     a.CG = ceil_div(g.Co, RM) < cg_max ? ceil_div(g.Co, RM) : cg_max;
     a.TM = a.CG * RM;
     a.TMP = a.TM + 4;
-    const int threads_target = hint.threads > 0 ? hint.threads : 128;
     int segs_target = threads_target / a.CG;
     if (segs_target < 1) segs_target = 1;
     const int spr_full = ceil_div(g.Wo, RW);   // segments in a full output row
@@ -201,8 +202,10 @@ static int plan_fwd_t(const Geom& g, const float* out, const TileHint& hint, Fwd
         a.TH = (2 * d > rows_target || d == g.Ho) ? d : (rows_target < g.Ho ? rows_target : g.Ho);
     }
     a.TI = 1;
+    int ti_budget = 1;   // tile images before clamping to the batch: the chunk size must not depend on N
     if (a.TH == g.Ho) {
         a.TI = rows_target / a.TH;
+        ti_budget = a.TI > 1 ? a.TI : 1;
         if (a.TI < 1) a.TI = 1;
         if (a.TI > g.N) a.TI = g.N;
         if (a.TI < 1) a.TI = 1;
@@ -228,10 +231,10 @@ static int plan_fwd_t(const Geom& g, const float* out, const TileHint& hint, Fwd
     a.CH_STRIDE = a.TI * a.ROWS_PITCH;
     // channel chunk: fill the shared-memory budget (two CTAs per SM) without exceeding Ci
     const int budget_floats = (hint.smem_kb > 0 ? hint.smem_kb : 100) * 1024 / 4;
-    int ck = hint.ck > 0 ? hint.ck : 8;
+    int ck = hint.ck > 0 ? hint.ck : (KS == 1 ? 32 : 16);
     if (ck > g.Ci) ck = g.Ci;
     while (ck > 1) {
-        const int need = 2 * (round_up(ck * a.CH_STRIDE, 4) + round_up(ck * KS * KS, 8) * a.TMP);
+        const int need = 2 * (round_up(ck * ti_budget * a.ROWS_PITCH, 4) + round_up(ck * KS * KS, 8) * a.TMP);
         if (need <= budget_floats) break;
         --ck;
     }
@@ -282,13 +285,13 @@ static void choose_fwd_tile(const Geom& g, const TileHint& hint, int& rw, int& r
     if (hint.rw > 0 && hint.rm > 0) { rw = hint.rw; rm = hint.rm; return; }
     if ((g.Wo % 8 != 0) && (g.Wo % 7 == 0)) { rw = 7; rm = 8; return; }
     if (g.Wo % 4 != 0) { rw = 8; rm = 8; return; }
-    const long long want = 75000;
     const int cand[3][2] = {{8, 8}, {8, 4}, {4, 4}};
+    const long long want[3] = {100000, 30000, 0};     // thresholds found by sweeping the ResNet-20 layer shapes
     for (int c = 0; c < 3; ++c) {
         rw = cand[c][0]; rm = cand[c][1];
         if (g.Wo % rw != 0 && rw == 8) continue;
         const long long threads = (long long)g.N * g.Ho * ceil_div(g.Wo, rw) * ceil_div(g.Co, rm);
-        if (threads >= want) return;
+        if (threads >= want[c]) return;
     }
 }
 
