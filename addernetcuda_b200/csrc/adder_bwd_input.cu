@@ -54,9 +54,21 @@ __global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
 
     uint32_t cig, seg, t2, wsx, pw, ws, img, hr;
     a.d_segs.divmod(tid, cig, seg);
-    a.d_spr.divmod(seg, t2, wsx);
-    a.d_sprc.divmod(wsx, pw, ws);
-    a.d_th.divmod(t2, img, hr);
+    if (S > 1 && a.class_major) {
+        // stride > 1: order the segments by (row offset mod S, column parity) first, so that the lanes of a
+        // warp share one set of valid taps instead of diverging over up to S*S different ones
+        uint32_t t, hr2, cls;
+        a.d_sprc.divmod(seg, t, ws);
+        a.d_ths.divmod(t, t2, hr2);
+        a.d_ti.divmod(t2, cls, img);       // class slowest: TI*(TH/S)*SPRC consecutive segments share it
+        pw = cls % S;
+        hr = hr2 * S + cls / S;
+        wsx = 0;
+    } else {
+        a.d_spr.divmod(seg, t2, wsx);
+        a.d_sprc.divmod(wsx, pw, ws);
+        a.d_th.divmod(t2, img, hr);
+    }
     const bool active = (int)cig < a.CGI;
     const int n = n0 + img, hi = hi0 + hr;
     const int q0 = wq0 + ws * RW;                  // class-pixel index of the thread's first pixel
@@ -131,10 +143,11 @@ __global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
             }
         }
         if (active) {
+            const int ncol = min(a.CKO, a.g.Co - c * a.CKO);
             const float* gimg = gs + img * a.pd.ROWS_PITCH;
             const float* wt = Wt + (c & 1) * a.ws_stage + cig * RC;
 #pragma unroll 1
-            for (int col = 0; col < a.CKO; ++col) {
+            for (int col = 0; col < ncol; ++col) {
                 const float* gch = gimg + col * a.CH_STRIDE;
                 const float* wch = wt + col * KK * a.TCIP;
                 if constexpr (S == 1) {
@@ -281,7 +294,7 @@ static int plan_gx_t(const Geom& g, const TileHint& hint, GxPlan& p) {
     p.ks = KS; p.s = S; p.rw = RW; p.rc = RC; p.fast = FAST;
     a.g = g;
     const int threads_target = hint.threads > 0 ? hint.threads : 256;
-    const int cg_max = hint.cg > 0 ? hint.cg : 4;
+    const int cg_max = hint.cg > 0 ? hint.cg : (S > 1 ? 2 : (g.Ci >= 128 ? 8 : 4));   // stride > 1: more pixels per CTA, one tap class per warp
     a.CGI = ceil_div(g.Ci, RC) < cg_max ? ceil_div(g.Ci, RC) : cg_max;
     a.TCI = a.CGI * RC;
     a.TCIP = a.TCI + 4;
@@ -292,6 +305,11 @@ static int plan_gx_t(const Geom& g, const TileHint& hint, GxPlan& p) {
     a.SPRC = sprc_full * S <= segs_target ? sprc_full : (segs_target / S > 0 ? segs_target / S : 1);
     a.SPR = a.SPRC * S;
     int rows_target = segs_target / a.SPR;
+    {   // short tiles won the sweeps (more CTAs, smaller patches), but keep at least a warp of segments
+        int cap = 8 * S;
+        if (cap * a.SPR < 32) cap = ceil_div(32, a.SPR);
+        if (rows_target > cap) rows_target = cap;
+    }
     if (rows_target < 1) rows_target = 1;
     if (hint.th > 0) {
         a.TH = hint.th < g.H ? hint.th : g.H;
@@ -302,7 +320,7 @@ static int plan_gx_t(const Geom& g, const TileHint& hint, GxPlan& p) {
     a.TI = 1;
     int ti_budget = 1;   // tile images before clamping to the batch: the chunk size must not depend on N
     if (a.TH == g.H) {
-        a.TI = rows_target / a.TH;
+        a.TI = segs_target / (a.TH * a.SPR);
         ti_budget = a.TI > 1 ? a.TI : 1;
         if (a.TI < 1) a.TI = 1;
         if (a.TI > g.N) a.TI = g.N;
@@ -331,15 +349,17 @@ static int plan_gx_t(const Geom& g, const TileHint& hint, GxPlan& p) {
     pd.ROWS_PITCH = pd.ROWS * pd.PITCH;
     a.CH_STRIDE = a.TI * pd.ROWS_PITCH;
     a.g1_size = FAST ? a.CH_STRIDE : 0;
-    const int budget_floats = (hint.smem_kb > 0 ? hint.smem_kb : 100) * 1024 / 4;
+    // shared memory per CTA in proportion to its threads, so that about 16 warps stay resident per SM
+    const int budget_floats = (hint.smem_kb > 0 ? hint.smem_kb : (threads <= 64 ? 26 : threads <= 128 ? 52 : 104)) * 1024 / 4;
     int cko = hint.ck > 0 ? hint.ck : (KS == 1 ? 64 : 16);
     if (cko > g.Co) cko = g.Co;
     while (cko > 1) {
         const int need = 2 * (round_up(cko * ti_budget * pd.ROWS_PITCH, 4) + cko * KS * KS * a.TCIP) +
-                         (FAST ? ti_budget * pd.ROWS_PITCH : 0) + RC * RW * 256;
+                         (FAST ? ti_budget * pd.ROWS_PITCH : 0) + RC * RW * threads;
         if (need <= budget_floats) break;
         --cko;
     }
+    cko = ceil_div(g.Co, ceil_div(g.Co, cko));    // same number of chunks, evenly sized: no padded channels
     a.CKO = cko;
     pd.CH = cko;
     a.gs_stage = round_up(cko * a.CH_STRIDE, 4);
@@ -355,6 +375,9 @@ static int plan_gx_t(const Geom& g, const TileHint& hint, GxPlan& p) {
     a.d_spr = FastDiv(a.SPR);
     a.d_sprc = FastDiv(a.SPRC);
     a.d_th = FastDiv(a.TH);
+    a.class_major = (S > 1 && a.TH % S == 0) ? 1 : 0;
+    a.d_ths = FastDiv(a.class_major ? a.TH / S : 1);
+    a.d_ti = FastDiv(a.TI);
     a.d_tcikk = FastDiv(a.TCI * KS * KS);
     a.d_kk = FastDiv(KS * KS);
     const long long gxd = (long long)ceil_div(g.N, a.TI) * a.tiles_h * a.tiles_w;

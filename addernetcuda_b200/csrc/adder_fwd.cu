@@ -90,8 +90,9 @@ __global__ void __launch_bounds__(256, 2) adder_fwd_kernel(const FwdArgs a) {
         if (active) {
             const float* xs = Xs + (c & 1) * a.xs_stage + xoff;
             const float* wsm = Ws + (c & 1) * a.ws_stage + cg * RM;
+            const int nch = min(a.CK, a.g.Ci - c * a.CK);
 #pragma unroll 1
-            for (int cil = 0; cil < a.CK; ++cil) {
+            for (int cil = 0; cil < nch; ++cil) {
 #pragma unroll
                 for (int kh = 0; kh < KS; ++kh) {
                     float xv[XW];
@@ -230,6 +231,7 @@ static int plan_fwd_t(const Geom& g, const float* out, const TileHint& hint, Fwd
     a.pd.d_cols = FastDiv(a.IN_COLS); a.pd.d_rows = FastDiv(a.IN_ROWS);
     a.CH_STRIDE = a.TI * a.ROWS_PITCH;
     // channel chunk: fill the shared-memory budget (two CTAs per SM) without exceeding Ci
+    // shared memory per CTA in proportion to its threads, so that about 16 warps stay resident per SM
     const int budget_floats = (hint.smem_kb > 0 ? hint.smem_kb : 100) * 1024 / 4;
     int ck = hint.ck > 0 ? hint.ck : (KS == 1 ? 32 : 16);
     if (ck > g.Ci) ck = g.Ci;
@@ -238,6 +240,7 @@ static int plan_fwd_t(const Geom& g, const float* out, const TileHint& hint, Fwd
         if (need <= budget_floats) break;
         --ck;
     }
+    ck = ceil_div(g.Ci, ceil_div(g.Ci, ck));      // same number of chunks, evenly sized: no padded channels
     a.CK = ck;
     a.pd.CH = ck;
     a.wkk_pad = round_up(a.CK * KS * KS, 8);

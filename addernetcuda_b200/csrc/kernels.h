@@ -40,8 +40,8 @@ struct GxArgs {
     float* gx;           // [N,Ci,H,W]
     PatchDims pd;        // patch of g staged per output-channel chunk
     int TI, TH, SPRC, SPR, SEGS, CGI, TCI, TCIP, CKO, CH_STRIDE;
-    int gs_stage, ws_stage, g1_size, tiles_h, tiles_w, accumulate;
-    FastDiv d_tiles_h, d_tiles_w, d_segs, d_spr, d_sprc, d_th, d_tcikk, d_kk;
+    int gs_stage, ws_stage, g1_size, tiles_h, tiles_w, accumulate, class_major;
+    FastDiv d_tiles_h, d_tiles_w, d_segs, d_spr, d_sprc, d_th, d_ths, d_ti, d_tcikk, d_kk;
 };
 
 struct GwArgs {
