@@ -74,8 +74,14 @@ __global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
     const int q0 = wq0 + ws * RW;                  // class-pixel index of the thread's first pixel
     const int HW = a.g.H * a.g.W;
 
+    constexpr bool PACKED = FAST && S == 1 && (RC % 2 == 0);
     float xv[RC][RW];
     float acc[RC][RW];
+    uint64_t acc2[RC / 2][RW];
+#pragma unroll
+    for (int c = 0; c < RC / 2; ++c)
+#pragma unroll
+        for (int j = 0; j < RW; ++j) acc2[c][j] = 0ull;
 #pragma unroll
     for (int c = 0; c < RC; ++c) {
         const int ci = ci0 + cig * RC + c;
@@ -157,6 +163,23 @@ __global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
                         const float* gr = gcol + ((int)hr + KS - 1 - kh) * a.pd.PITCH;
                         float gv[RW + KS - 1];
                         load_run<RW + KS - 1, (RW % 4 == 0)>(gv, gr);
+                        if constexpr (PACKED) {
+                            // two channels per fused multiply-add: (s0, s1) * (g, g) + (acc0, acc1)
+                            uint64_t g2[RW + KS - 1];
+#pragma unroll
+                            for (int i = 0; i < RW + KS - 1; ++i) g2[i] = pack2(gv[i], gv[i]);
+#pragma unroll
+                            for (int kw = 0; kw < KS; ++kw) {
+                                const float4 t = *reinterpret_cast<const float4*>(wch + (kh * KS + kw) * a.TCIP);
+                                const float wv[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                                for (int cc = 0; cc < RC; cc += 2)
+#pragma unroll
+                                    for (int j = 0; j < RW; ++j)
+                                        acc2[cc / 2][j] = fma2(pack2(gx_term<true>(wv[cc], xv[cc][j]), gx_term<true>(wv[cc + 1], xv[cc + 1][j])),
+                                                               g2[j + KS - 1 - kw], acc2[cc / 2][j]);
+                            }
+                        } else {
 #pragma unroll
                         for (int kw = 0; kw < KS; ++kw) {
                             const float4 t = *reinterpret_cast<const float4*>(wch + (kh * KS + kw) * a.TCIP);
@@ -166,6 +189,7 @@ __global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
 #pragma unroll
                                 for (int j = 0; j < RW; ++j)
                                     acc[cc][j] = fmaf(gx_term<FAST>(wv[cc], xv[cc][j]), gv[j + KS - 1 - kw], acc[cc][j]);
+                        }
                         }
                     }
                 } else {
@@ -196,6 +220,15 @@ __global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
             // Two-level summation: the chunk's partial sums are folded into per-thread running totals
             // kept in shared memory, so a long sum over output channels loses far less precision than one
             // running fp32 accumulator would.
+            if constexpr (PACKED) {
+#pragma unroll
+                for (int cc = 0; cc < RC; cc += 2)
+#pragma unroll
+                    for (int j = 0; j < RW; ++j) {
+                        unpack2(acc2[cc / 2][j], acc[cc][j], acc[cc + 1][j]);
+                        acc2[cc / 2][j] = 0ull;
+                    }
+            }
 #pragma unroll
             for (int cc = 0; cc < RC; ++cc)
 #pragma unroll

@@ -342,7 +342,7 @@ static GwPlan plan_gw_t(const Geom& g, const TileHint& hint) {
     // output tile
     const int cgo_max = hint.cg > 0 ? hint.cg : (KS == 1 ? 8 : 8);
     a.CGO = ceil_div(g.Co, RM) < cgo_max ? ceil_div(g.Co, RM) : cgo_max;
-    const int cgc_max = 8;
+    const int cgc_max = 16 / RC < 8 ? 8 : 16 / RC;
     a.CGC = ceil_div(g.Ci, RC) < cgc_max ? ceil_div(g.Ci, RC) : cgc_max;
     a.TM = a.CGO * RM;
     a.TCI = a.CGC * RC;
@@ -444,6 +444,7 @@ static GwPlan plan_gw_t(const Geom& g, const TileHint& hint) {
 
 static GwPlan plan_gw(const Geom& g, const TileHint& hint) {
     const bool rw7 = (g.Wo % 8 != 0) && (g.Wo % 7 == 0);
+    if (g.k == 3 && g.stride == 1 && !rw7 && hint.rm == 1) return plan_gw_t<3, 1, 8, 4, 1>(g, hint);
     if (g.k == 3 && g.stride == 1) return rw7 ? plan_gw_t<3, 1, 7, 4, 2>(g, hint) : plan_gw_t<3, 1, 8, 4, 2>(g, hint);
     if (g.k == 3 && g.stride == 2) return rw7 ? plan_gw_t<3, 2, 7, 4, 2>(g, hint) : plan_gw_t<3, 2, 8, 4, 2>(g, hint);
     if (g.k == 1 && g.stride == 1) return rw7 ? plan_gw_t<1, 1, 7, 8, 4>(g, hint) : plan_gw_t<1, 1, 8, 8, 4>(g, hint);
@@ -506,7 +507,8 @@ int launch_gw(const Geom& g, const float* gout, const float* x, const float* w, 
 
     const bool rw7 = (g.Wo % 8 != 0) && (g.Wo % 7 == 0);
     int st = ADDER_ERR_UNSUPPORTED;
-    if (g.k == 3 && g.stride == 1) st = rw7 ? launch_main_t<3, 1, 7, 4, 2>(p, stream) : launch_main_t<3, 1, 8, 4, 2>(p, stream);
+    if (g.k == 3 && g.stride == 1 && !rw7 && hint.rm == 1) st = launch_main_t<3, 1, 8, 4, 1>(p, stream);
+    else if (g.k == 3 && g.stride == 1) st = rw7 ? launch_main_t<3, 1, 7, 4, 2>(p, stream) : launch_main_t<3, 1, 8, 4, 2>(p, stream);
     else if (g.k == 3 && g.stride == 2) st = rw7 ? launch_main_t<3, 2, 7, 4, 2>(p, stream) : launch_main_t<3, 2, 8, 4, 2>(p, stream);
     else if (g.k == 1 && g.stride == 1) st = rw7 ? launch_main_t<1, 1, 7, 8, 4>(p, stream) : launch_main_t<1, 1, 8, 8, 4>(p, stream);
     else if (g.k == 1 && g.stride == 2) st = rw7 ? launch_main_t<1, 2, 7, 8, 4>(p, stream) : launch_main_t<1, 2, 8, 8, 4>(p, stream);

@@ -12,6 +12,9 @@
 // innermost, so a thread's RM weights are two 128-bit loads that the whole warp shares).  For
 // each (ci, kh) a thread loads the (RW-1)*S+KS input values its segment touches once and slides
 // the KS taps over them in registers: two FP32 instructions per |x-w| term (subtract, add-abs).
+#ifndef ADDER_FWD_PACKED
+#define ADDER_FWD_PACKED 1
+#endif
 #include "common.cuh"
 #include "kernels.h"
 #include "patch_fill.cuh"
@@ -98,6 +101,11 @@ __global__ void __launch_bounds__(256, 2) adder_fwd_kernel(const FwdArgs a) {
                     float xv[XW];
                     const float* xr = xs + cil * a.CH_STRIDE + kh * a.PITCH;
                     load_run<XW, (RW % 4 == 0)>(xv, xr);
+#if ADDER_FWD_PACKED
+                    uint64_t nx2[XW];
+#pragma unroll
+                    for (int i = 0; i < XW; ++i) nx2[i] = pack2(-xv[i], -xv[i]);
+#endif
 #pragma unroll
                     for (int kw = 0; kw < KS; ++kw) {
                         const float* wr = wsm + (cil * KK + kh * KS + kw) * a.TMP;
@@ -107,10 +115,25 @@ __global__ void __launch_bounds__(256, 2) adder_fwd_kernel(const FwdArgs a) {
                             const float4 t = *reinterpret_cast<const float4*>(wr + m4);
                             wv[m4] = t.x; wv[m4 + 1] = t.y; wv[m4 + 2] = t.z; wv[m4 + 3] = t.w;
                         }
+#if ADDER_FWD_PACKED
+                        // |w - x| for two channels at once: one packed subtract, then two scalar add-abs
+#pragma unroll
+                        for (int m = 0; m < RM; m += 2) {
+                            const uint64_t w2 = pack2(wv[m], wv[m + 1]);
+#pragma unroll
+                            for (int j = 0; j < RW; ++j) {
+                                float d0, d1;
+                                unpack2(add2(w2, nx2[j * S + kw]), d0, d1);
+                                acc[m][j] += fabsf(d0);
+                                acc[m + 1][j] += fabsf(d1);
+                            }
+                        }
+#else
 #pragma unroll
                         for (int m = 0; m < RM; ++m)
 #pragma unroll
                             for (int j = 0; j < RW; ++j) acc[m][j] += fabsf(xv[j * S + kw] - wv[m]);
+#endif
                     }
                 }
             }
