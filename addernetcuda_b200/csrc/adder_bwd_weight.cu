@@ -22,10 +22,13 @@
 #include "patch_fill.cuh"
 #include <cstdio>
 
+#ifndef GW_MIN_BLOCKS
+#define GW_MIN_BLOCKS 2
+#endif
 namespace adder {
 
 template <int KS, int S, int RW, int RM, int RC>
-__global__ void __launch_bounds__(256, 2) adder_gw_kernel(const GwArgs a) {
+__global__ void __launch_bounds__(256, GW_MIN_BLOCKS) adder_gw_kernel(const GwArgs a) {
     constexpr int KK = KS * KS;
     constexpr int XW = (RW - 1) * S + KS;
     constexpr bool VEC = (RW % 4 == 0);      // segment starts are 16-byte aligned in both patches
