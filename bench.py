@@ -48,6 +48,12 @@ RESNET20_LAYERS = [
 ]
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, 16->16 32x32 k3 layer at batch 256 (ncu --set full)
+NCU_DRAM_BYTES = {"adder_fwd_kernel": 16816640, "adder_gx_kernel": 33620992, "adder_gw_kernel": 33589760}
+# 4*(|x|+|w|+|out|), 4*(|g|+|x|+|w|+|gx|), 4*(|g|+|x|+|w|+|gw|) for that layer
+ALGO_BYTES_16x16 = {"adder_fwd_kernel": 33563648, "adder_gx_kernel": 50340864, "adder_gw_kernel": 33572864}
+
+
 def triples(n, shape):
     ci, co, h, w, s, k, p = shape
     ho, wo = (h - k + 2 * p) // s + 1, (w - k + 2 * p) // s + 1
@@ -352,7 +358,10 @@ def run_gpu_arm(args):
             "achieved": achieved / 1e12, "peak": fp32_peak / 1e12, "unit": "TFLOP/s", "frac": achieved / fp32_peak,
             "peak_source": f"2*128*{sms} SMs*{f_max:.0f} MHz (FP32 CUDA-core FMA peak; MEASURED_PEAKS.json holds no SIMT figure)",
             "ops_rule": "3 ops per (co,k,pixel) triple per pass", "launches": 20, "ms_total": tot[dom],
-            "traffic": None,
+            "traffic": NCU_DRAM_BYTES.get(dom_kernel),
+            "traffic_note": "dram read+write bytes of ONE launch on the 16->16 32x32 layer at batch 256 from the ncu "
+                            "capture summarised in profiles/adder_kernels_c16to16_32x32_b256.txt; algorithmic bytes of "
+                            "that launch: %d" % ALGO_BYTES_16x16.get(dom_kernel, 0),
         }
         line["adder_conv"] = {
             "workload": "the 20 adder layers of ResNet-20 at batch 256, kernels timed alone (L2 flushed)",
