@@ -41,7 +41,7 @@ SIGNATURES = {
     "adder_b200_backward_col": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                         c_void_p, c_size_t, c_void_p]),
     "adder_b200_batchnorm_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
-    "adder_b200_batchnorm_forward": (c_int, [c_void_p] * 9 + [c_float, c_float, c_int, c_void_p, c_size_t,
+    "adder_b200_batchnorm_forward": (c_int, [c_void_p] * 10 + [c_float, c_float, c_int, c_void_p, c_size_t,
                                              c_int, c_int, c_int, c_void_p]),
     "adder_b200_batchnorm_backward": (c_int, [c_void_p] * 10 + [c_int, c_void_p, c_size_t, c_int, c_int, c_int,
                                               c_void_p]),

@@ -17,7 +17,7 @@ from . import _lib, adder_cuda
 
 class _BNFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, y, gamma, beta, residual, running_mean, running_var, eps, momentum, relu):
+    def forward(ctx, y, gamma, beta, residual, running_mean, running_var, num_batches, eps, momentum, relu):
         y = y.contiguous()
         n, c, h, w = y.shape
         dev = y.device
@@ -33,6 +33,7 @@ class _BNFunction(torch.autograd.Function):
                 z.data_ptr(), mean.data_ptr(), invstd.data_ptr(),
                 running_mean.data_ptr() if running_mean is not None else None,
                 running_var.data_ptr() if running_var is not None else None,
+                num_batches.data_ptr() if num_batches is not None else None,
                 float(eps), float(momentum), int(relu), ws.data_ptr(), ws.numel(), n, c, h * w,
                 adder_cuda._stream(dev)), "adder_b200_batchnorm_forward")
         ctx.save_for_backward(y, z if relu else None, gamma, mean, invstd)
@@ -58,7 +59,7 @@ class _BNFunction(torch.autograd.Function):
                 mean.data_ptr(), invstd.data_ptr(), dy.data_ptr(), dres.data_ptr() if dres is not None else None,
                 dgamma.data_ptr(), dbeta.data_ptr(), int(ctx.relu), ws.data_ptr(), ws.numel(), n, c, h * w,
                 adder_cuda._stream(dev)), "adder_b200_batchnorm_backward")
-        return dy, dgamma, dbeta, dres, None, None, None, None, None
+        return dy, dgamma, dbeta, dres, None, None, None, None, None, None
 
 
 class FusedBatchNorm2d(nn.BatchNorm2d):
@@ -72,7 +73,5 @@ class FusedBatchNorm2d(nn.BatchNorm2d):
             if residual is not None:
                 out = out + residual
             return torch.relu(out) if relu else out
-        if self.num_batches_tracked is not None:
-            self.num_batches_tracked.add_(1)
         return _BNFunction.apply(y, self.weight, self.bias, residual, self.running_mean, self.running_var,
-                                 self.eps, self.momentum, relu)
+                                 self.num_batches_tracked, self.eps, self.momentum, relu)

@@ -174,7 +174,7 @@ __global__ void __launch_bounds__(256, GW_MIN_BLOCKS) adder_gw_kernel(const GwAr
 }
 
 constexpr int FIN_THREADS = 256;
-constexpr int FIN_OUT = 32;                       // gradient elements per reduce block
+constexpr int FIN_OUT = 8;                        // gradient elements per reduce block
 constexpr int FIN_LANES = FIN_THREADS / FIN_OUT;  // threads that share one element and split the slices
 constexpr int FUSED_FINISH_MAX = 1 << 17;         // gradients up to this many elements finish in one kernel
 

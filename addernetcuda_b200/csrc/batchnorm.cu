@@ -78,6 +78,7 @@ __global__ void __launch_bounds__(BN_THREADS) bn_stats_kernel(const float* __res
 struct BnFwdArgs {
     const float* y; const float* gamma; const float* beta; const float* residual;
     float* z; float* save_mean; float* save_invstd; float* running_mean; float* running_var;
+    long long* num_batches;   // optional counter (nn.BatchNorm2d.num_batches_tracked), incremented once per call
     const double* part;
     float eps, momentum;
     int relu;
@@ -102,6 +103,7 @@ __global__ void __launch_bounds__(BN_THREADS) bn_apply_kernel(BnFwdArgs a, BnGeo
         const float invstd = (float)(1.0 / sqrt(var + (double)a.eps));
         s_mean = (float)mean;
         s_invstd = invstd;
+        if (sp == 0 && c == 0 && a.num_batches != nullptr) *a.num_batches += 1;
         if (sp == 0) {
             a.save_mean[c] = (float)mean;
             a.save_invstd[c] = invstd;
@@ -279,8 +281,9 @@ size_t adder_b200_batchnorm_workspace_bytes(int n, int c, int hw) {
 
 int adder_b200_batchnorm_forward(const float* y, const float* gamma, const float* beta, const float* residual,
                                  float* z, float* save_mean, float* save_invstd, float* running_mean,
-                                 float* running_var, float eps, float momentum, int relu, void* workspace,
-                                 size_t workspace_bytes, int n, int c, int hw, void* stream) {
+                                 float* running_var, long long* num_batches_tracked, float eps, float momentum,
+                                 int relu, void* workspace, size_t workspace_bytes, int n, int c, int hw,
+                                 void* stream) {
     BnGeom g;
     const int st = bn_geom(n, c, hw, &g);
     if (st != ADDER_OK) return st;
@@ -294,7 +297,8 @@ int adder_b200_batchnorm_forward(const float* y, const float* gamma, const float
     double* part = static_cast<double*>(workspace);
     const dim3 grid(g.splits, c);
     bn_stats_kernel<<<grid, BN_THREADS, 0, s>>>(y, g, part);
-    BnFwdArgs a{y, gamma, beta, residual, z, save_mean, save_invstd, running_mean, running_var, part, eps, momentum, relu};
+    BnFwdArgs a{y, gamma, beta, residual, z, save_mean, save_invstd, running_mean, running_var, num_batches_tracked,
+                part, eps, momentum, relu};
     bn_apply_kernel<<<grid, BN_THREADS, 0, s>>>(a, g);
     return cudaGetLastError() == cudaSuccess ? ADDER_OK : ADDER_ERR_CUDA;
 }

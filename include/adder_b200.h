@@ -148,14 +148,15 @@ ADDER_API int adder_b200_backward_col(const float* grad_y, const float* x, const
  * NCHW fp32 tensors [n, c, hw]: batch statistics per channel (biased variance for normalising,
  * unbiased for running_var, as torch.nn.BatchNorm2d), z = gamma*(y-mean)*invstd + beta
  * [+ residual] [then ReLU].  save_mean / save_invstd [c] are outputs kept for the backward pass;
- * running_mean / running_var [c] may both be NULL.  Workspace: 16-byte aligned scratch of
+ * running_mean / running_var [c] may both be NULL; num_batches_tracked (one int64, may be NULL) is
+ * incremented by one.  Workspace: 16-byte aligned scratch of
  * adder_b200_batchnorm_workspace_bytes(); tensors must be 16-byte aligned when hw % 4 == 0. */
 ADDER_API size_t adder_b200_batchnorm_workspace_bytes(int n, int c, int hw);
 ADDER_API int adder_b200_batchnorm_forward(const float* y, const float* gamma, const float* beta,
                                            const float* residual, float* z, float* save_mean, float* save_invstd,
-                                           float* running_mean, float* running_var, float eps, float momentum,
-                                           int relu, void* workspace, size_t workspace_bytes, int n, int c, int hw,
-                                           void* stream);
+                                           float* running_mean, float* running_var, long long* num_batches_tracked,
+                                           float eps, float momentum, int relu, void* workspace,
+                                           size_t workspace_bytes, int n, int c, int hw, void* stream);
 /* Backward of the above: dz is the gradient of z; with relu != 0 it is first masked by z > 0 (z: the
  * forward output).  Outputs: dy, dgamma[c], dbeta[c] and, when dresidual != NULL, the gradient of the
  * residual input (= the masked dz). */
