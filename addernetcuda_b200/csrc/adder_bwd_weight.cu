@@ -321,6 +321,7 @@ struct GwPlan {
     size_t smem;
     int fin_blocks;
     int status;
+    bool use_1x1 = false;   // 1x1 stride-1 layers with enough channels take the GEMM-style kernel
 };
 
 static int sm_count() {
@@ -445,7 +446,18 @@ static GwPlan plan_gw_t(const Geom& g, const TileHint& hint) {
     return p;
 }
 
+static GwPlan plan_gw_generic(const Geom& g, const TileHint& hint);
+
 static GwPlan plan_gw(const Geom& g, const TileHint& hint) {
+    GwPlan p = plan_gw_generic(g, hint);
+    if (p.status == ADDER_OK && gw1x1_applicable(g) && hint.rm != 9) {
+        p.use_1x1 = true;
+        p.a.splits = gw1x1_splits(g);
+    }
+    return p;
+}
+
+static GwPlan plan_gw_generic(const Geom& g, const TileHint& hint) {
     const bool rw7 = (g.Wo % 8 != 0) && (g.Wo % 7 == 0);
     if (g.k == 3 && g.stride == 1 && !rw7 && hint.rm == 1) return plan_gw_t<3, 1, 8, 4, 1>(g, hint);
     if (g.k == 3 && g.stride == 1) return rw7 ? plan_gw_t<3, 1, 7, 4, 2>(g, hint) : plan_gw_t<3, 1, 8, 4, 2>(g, hint);
@@ -465,10 +477,10 @@ int describe_gw(const Geom& g, const TileHint& hint, char* buf, size_t n) {
     const GwArgs& a = p.a;
     snprintf(buf, n,
              "gw k=%d s=%d CGO=%d CGC=%d TM=%d TCI=%d PL=%d TI=%d TH=%d SPR=%d SEGS=%d xrows=%d xcols=%d xpitch=%d gpitch=%d "
-             "threads=%d smem=%zu tiles=%d splits=%d tiles_per_split=%d out_tiles=%d fin_blocks=%d status=%d",
+             "threads=%d smem=%zu tiles=%d splits=%d tiles_per_split=%d out_tiles=%d fin_blocks=%d gemm1x1=%d status=%d",
              g.k, g.stride, a.CGO, a.CGC, a.TM, a.TCI, a.PL, a.TI, a.TH, a.SPR, a.SEGS, a.pdx.ROWS, a.pdx.COLS, a.pdx.PITCH,
              a.pdg.PITCH, p.threads, p.smem, a.tiles_total, a.splits, a.tiles_per_split,
-             ceil_div(g.Co, a.TM) * a.n_ci_tiles, p.fin_blocks, p.status);
+             ceil_div(g.Co, a.TM) * a.n_ci_tiles, p.fin_blocks, (int)p.use_1x1, p.status);
     return ADDER_OK;
 }
 
@@ -510,7 +522,8 @@ int launch_gw(const Geom& g, const float* gout, const float* x, const float* w, 
 
     const bool rw7 = (g.Wo % 8 != 0) && (g.Wo % 7 == 0);
     int st = ADDER_ERR_UNSUPPORTED;
-    if (g.k == 3 && g.stride == 1 && !rw7 && hint.rm == 1) st = launch_main_t<3, 1, 8, 4, 1>(p, stream);
+    if (p.use_1x1) st = launch_gw1x1(g, gout, x, p.a.part, p.a.gsum_part, ticket, p.a.splits, stream);
+    else if (g.k == 3 && g.stride == 1 && !rw7 && hint.rm == 1) st = launch_main_t<3, 1, 8, 4, 1>(p, stream);
     else if (g.k == 3 && g.stride == 1) st = rw7 ? launch_main_t<3, 1, 7, 4, 2>(p, stream) : launch_main_t<3, 1, 8, 4, 2>(p, stream);
     else if (g.k == 3 && g.stride == 2) st = rw7 ? launch_main_t<3, 2, 7, 4, 2>(p, stream) : launch_main_t<3, 2, 8, 4, 2>(p, stream);
     else if (g.k == 1 && g.stride == 1) st = rw7 ? launch_main_t<1, 1, 7, 8, 4>(p, stream) : launch_main_t<1, 1, 8, 8, 4>(p, stream);

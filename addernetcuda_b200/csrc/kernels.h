@@ -80,6 +80,11 @@ int launch_gw(const Geom& g, const float* gout, const float* x, const float* w, 
               float* out_norm, int accumulate, void* workspace, size_t workspace_bytes, const TileHint& hint,
               cudaStream_t s);
 
+bool gw1x1_applicable(const Geom& g);
+int gw1x1_splits(const Geom& g);
+int launch_gw1x1(const Geom& g, const float* gout, const float* x, float* part, float* gsum_part,
+                 unsigned int* ticket, int splits, cudaStream_t stream);
+
 int describe_fwd(const Geom& g, const TileHint& hint, char* buf, size_t n);
 int describe_gx(const Geom& g, int fast, const TileHint& hint, char* buf, size_t n);
 int describe_gw(const Geom& g, const TileHint& hint, char* buf, size_t n);
