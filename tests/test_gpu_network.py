@@ -146,6 +146,29 @@ def test_graph_captured_step_equals_eager_step():
             assert torch.allclose(s0[k], s1[k], rtol=1e-4, atol=1e-5), k
 
 
+def test_eval_mode_forward_matches_oracle_network():
+    """Inference: eval-mode forward (running statistics) of the CUDA network equals the CPU oracle network
+    loaded from the same state dict, as a checkpoint trained with the reference would be used (test.py:68-90)."""
+    from addernetcuda_b200 import resnet as R
+    from oracle import adder_unfold as U
+    net = _build()
+    # make the running statistics non-trivial: two training steps
+    images, labels = resnet20_batch(16, SEED)
+    xg = torch.from_numpy(images).to(DEV)
+    net.train()
+    with torch.no_grad():
+        net(xg); net(xg * 0.5 + 0.1)
+    ref = R.resnet20(conv=U.adder2d)
+    ref.load_state_dict({k: v.cpu() for k, v in net.state_dict().items()})
+    net.eval(); ref.eval()
+    with torch.no_grad():
+        got = net(xg)
+        want = ref(torch.from_numpy(images))
+    ok, err, msg = O.compare("eval logits", got, want, abs_=2e-4)
+    print("   ", msg)
+    assert ok, msg
+
+
 def test_reference_checkpoint_keys_load():
     """A state dict with the reference's key names (as saved from a DataParallel wrapper, test.py:37-39)
     loads into the builder's network."""
