@@ -22,6 +22,9 @@
 #include "patch_fill.cuh"
 #include <cstdio>
 
+#ifndef GX_PACKED
+#define GX_PACKED 1
+#endif
 namespace adder {
 
 template <bool FAST>
@@ -74,7 +77,7 @@ __global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
     const int q0 = wq0 + ws * RW;                  // class-pixel index of the thread's first pixel
     const int HW = a.g.H * a.g.W;
 
-    constexpr bool PACKED = FAST && S == 1 && (RC % 2 == 0);
+    constexpr bool PACKED = GX_PACKED && FAST && S == 1 && (RC % 2 == 0);
     float xv[RC][RW];
     float acc[RC][RW];
     uint64_t acc2[RC / 2][RW];
