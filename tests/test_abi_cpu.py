@@ -120,7 +120,8 @@ def test_reference_model_files_import_unchanged_on_the_dropin():
         assert [tuple(v.shape) for v in r50.state_dict().values()] == [tuple(v.shape) for v in mine.state_dict().values()]
         with torch.device("meta"):
             importlib.import_module("vgg").vgg11_bn()
+            importlib.import_module("densenet").densenet_cifar()
     finally:
         sys.path.remove("/root/reference")
-        for mod in ("adder", "adder_cuda", "resnet20", "resnet50", "vgg"):
+        for mod in ("adder", "adder_cuda", "resnet20", "resnet50", "vgg", "densenet"):
             sys.modules.pop(mod, None)
