@@ -18,6 +18,7 @@ import argparse
 import importlib
 import json
 import math
+import os
 import sys
 from pathlib import Path
 
@@ -171,7 +172,7 @@ def resnet20_fixture(ref_path: str, batch: int, seed: int):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("ADDERNET_REFERENCE_DIR", "/root/reference"))
     ap.add_argument("--skip-resnet", action="store_true")
     ap.add_argument("--resnet-batches", default="16,256")
     a = ap.parse_args()

@@ -1,6 +1,7 @@
 """The C-ABI library loads without a GPU and exports exactly what include/adder_b200.h declares;
 host-side argument checks of the Python layer."""
 import ctypes
+import os
 import re
 from pathlib import Path
 
@@ -8,6 +9,8 @@ import pytest
 import torch
 
 ROOT = Path(__file__).resolve().parent.parent
+# checkout of the reference project, when one is available next to this repository (never needed on a GPU box)
+REFERENCE_DIR = os.environ.get("ADDERNET_REFERENCE_DIR", "/root/reference")
 
 
 def _declared():
@@ -98,7 +101,7 @@ def test_state_dict_keys_of_builders():
     assert sum(1 for k in n50.state_dict() if k.endswith(".adder")) == 52
 
 
-@pytest.mark.skipif(not Path("/root/reference/resnet20.py").exists(), reason="reference checkout not present")
+@pytest.mark.skipif(not Path(REFERENCE_DIR, "resnet20.py").exists(), reason="reference checkout not present")
 def test_reference_model_files_import_unchanged_on_the_dropin():
     """resnet20.py / resnet50.py / vgg.py of the reference only `import adder`; with the drop-in
     registered they build, and their state-dict keys equal this repository's builders'."""
@@ -107,7 +110,7 @@ def test_reference_model_files_import_unchanged_on_the_dropin():
     import addernetcuda_b200 as ab
     from addernetcuda_b200 import resnet as R
     ab.install_dropin()
-    sys.path.insert(0, "/root/reference")
+    sys.path.insert(0, REFERENCE_DIR)
     try:
         for mod in ("resnet20", "resnet50", "vgg"):
             sys.modules.pop(mod, None)
@@ -122,6 +125,6 @@ def test_reference_model_files_import_unchanged_on_the_dropin():
             importlib.import_module("vgg").vgg11_bn()
             importlib.import_module("densenet").densenet_cifar()
     finally:
-        sys.path.remove("/root/reference")
+        sys.path.remove(REFERENCE_DIR)
         for mod in ("adder", "adder_cuda", "resnet20", "resnet50", "vgg", "densenet"):
             sys.modules.pop(mod, None)
