@@ -33,6 +33,32 @@ __device__ __forceinline__ float gx_term(float wv, float xv) {
     return fminf(fmaxf(wv - xv, -1.f), 1.f);
 }
 
+// Stride-2 taps of one output channel for a thread whose pixels have row phase PH = (y+pad) mod 2 and
+// column phase PW = (x+pad) mod 2: only the taps kh = PH, PH+2, ... and kw = PW, PW+2, ... reach an
+// output pixel, so the loops are compile-time and nothing is predicated.  row0/col0 locate the tap
+// (PH, PW) in the shared-memory patch of g; later taps sit one row / one column before it.
+template <int KS, int RW, int RC, bool FAST, int PH, int PW>
+__device__ __forceinline__ void gx_taps_stride2(float (&acc)[RC][RW], const float (&xv)[RC][RW], const float* gch,
+                                                const float* wch, int row0, int col0, int pitch, int tcip) {
+#pragma unroll
+    for (int kh = PH; kh < KS; kh += 2) {
+        const float* gr = gch + (row0 - (kh - PH) / 2) * pitch + col0;
+#pragma unroll
+        for (int kw = PW; kw < KS; kw += 2) {
+            const float* gp = gr - (kw - PW) / 2;
+            float gv[RW];
+#pragma unroll
+            for (int j = 0; j < RW; ++j) gv[j] = gp[j];
+            const float4 t = *reinterpret_cast<const float4*>(wch + (kh * KS + kw) * tcip);
+            const float wv[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int cc = 0; cc < RC; ++cc)
+#pragma unroll
+                for (int j = 0; j < RW; ++j) acc[cc][j] = fmaf(gx_term<FAST>(wv[cc], xv[cc][j]), gv[j], acc[cc][j]);
+        }
+    }
+}
+
 template <int KS, int S, int RW, int RC, bool FAST>
 __global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
     constexpr int KK = KS * KS;
@@ -194,6 +220,16 @@ __global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
                                     acc[cc][j] = fmaf(gx_term<FAST>(wv[cc], xv[cc][j]), gv[j + KS - 1 - kw], acc[cc][j]);
                         }
                         }
+                    }
+                } else if constexpr (S == 2 && RC == 4) {
+                    const int ph = (hi + pad) & 1, pwp = ((int)pw + pad) & 1;
+                    const int row0 = (hi + pad - ph) / 2 - go_r0;
+                    const int col0 = q0 + ((int)pw + pad - pwp) / 2 - go_c0;
+                    switch (ph * 2 + pwp) {     // uniform across a warp when the segments are ordered by class
+                        case 0: gx_taps_stride2<KS, RW, RC, FAST, 0, 0>(acc, xv, gch, wch, row0, col0, a.pd.PITCH, a.TCIP); break;
+                        case 1: gx_taps_stride2<KS, RW, RC, FAST, 0, 1>(acc, xv, gch, wch, row0, col0, a.pd.PITCH, a.TCIP); break;
+                        case 2: gx_taps_stride2<KS, RW, RC, FAST, 1, 0>(acc, xv, gch, wch, row0, col0, a.pd.PITCH, a.TCIP); break;
+                        default: gx_taps_stride2<KS, RW, RC, FAST, 1, 1>(acc, xv, gch, wch, row0, col0, a.pd.PITCH, a.TCIP); break;
                     }
                 } else {
 #pragma unroll
