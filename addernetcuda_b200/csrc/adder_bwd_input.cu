@@ -8,7 +8,8 @@
 //
 // Work decomposition.  A CTA owns TCI = CGI*RC input channels and a tile of TI images x TH input
 // rows; a thread owns RC channels x RW input pixels of one row (for stride S > 1 the RW pixels are
-// S apart and share one column parity, so the set of valid taps is the same for all of them).  The
+// S apart and share one column parity, so the set of valid taps is the same for all of them, and the
+// segments of a CTA are ordered by (row, column) phase so that a warp runs one compile-time tap list).  The
 // thread keeps its RC*RW input values in registers for the whole kernel.  Output channels are
 // streamed in chunks of CKO through a double-buffered shared-memory stage holding the zero-filled
 // patch of g [CKO][TI*G_ROWS][PITCH] and the weights [CKO*k*k][TCI+4] (input channel innermost).

@@ -324,19 +324,6 @@ struct GwPlan {
     bool use_1x1 = false;   // 1x1 stride-1 layers with enough channels take the GEMM-style kernel
 };
 
-static int sm_count() {
-    int dev = 0, sms = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return 148;
-    return sms;
-}
-
-static int largest_divisor_le(int n, int limit) {
-    for (int d = limit < n ? limit : n; d >= 1; --d)
-        if (n % d == 0) return d;
-    return 1;
-}
-
 template <int KS, int S, int RW, int RM, int RC>
 static GwPlan plan_gw_t(const Geom& g, const TileHint& hint) {
     GwPlan p;
@@ -459,7 +446,6 @@ static GwPlan plan_gw(const Geom& g, const TileHint& hint) {
 
 static GwPlan plan_gw_generic(const Geom& g, const TileHint& hint) {
     const bool rw7 = (g.Wo % 8 != 0) && (g.Wo % 7 == 0);
-    if (g.k == 3 && g.stride == 1 && !rw7 && hint.rm == 1) return plan_gw_t<3, 1, 8, 4, 1>(g, hint);
     if (g.k == 3 && g.stride == 1) return rw7 ? plan_gw_t<3, 1, 7, 4, 2>(g, hint) : plan_gw_t<3, 1, 8, 4, 2>(g, hint);
     if (g.k == 3 && g.stride == 2) return rw7 ? plan_gw_t<3, 2, 7, 4, 2>(g, hint) : plan_gw_t<3, 2, 8, 4, 2>(g, hint);
     if (g.k == 1 && g.stride == 1) return rw7 ? plan_gw_t<1, 1, 7, 8, 4>(g, hint) : plan_gw_t<1, 1, 8, 8, 4>(g, hint);
@@ -523,7 +509,6 @@ int launch_gw(const Geom& g, const float* gout, const float* x, const float* w, 
     const bool rw7 = (g.Wo % 8 != 0) && (g.Wo % 7 == 0);
     int st = ADDER_ERR_UNSUPPORTED;
     if (p.use_1x1) st = launch_gw1x1(g, gout, x, p.a.part, p.a.gsum_part, ticket, p.a.splits, stream);
-    else if (g.k == 3 && g.stride == 1 && !rw7 && hint.rm == 1) st = launch_main_t<3, 1, 8, 4, 1>(p, stream);
     else if (g.k == 3 && g.stride == 1) st = rw7 ? launch_main_t<3, 1, 7, 4, 2>(p, stream) : launch_main_t<3, 1, 8, 4, 2>(p, stream);
     else if (g.k == 3 && g.stride == 2) st = rw7 ? launch_main_t<3, 2, 7, 4, 2>(p, stream) : launch_main_t<3, 2, 8, 4, 2>(p, stream);
     else if (g.k == 1 && g.stride == 1) st = rw7 ? launch_main_t<1, 1, 7, 8, 4>(p, stream) : launch_main_t<1, 1, 8, 8, 4>(p, stream);

@@ -142,18 +142,11 @@ bool gw1x1_applicable(const Geom& g) {
     return g.k == 1 && g.stride == 1 && g.pad == 0 && g.Co >= 64 && g.Ci >= 32 && g.N >= 1;
 }
 
-static int sm_count_1x1() {
-    int dev = 0, sms = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return 148;
-    return sms;
-}
-
 // Number of batch slices (CTAs per output tile): about three CTAs per SM in total.
 int gw1x1_splits(const Geom& g) {
     const int out_tiles = ceil_div(g.Co, G1_TM) * ceil_div(g.Ci, G1_TN);
     const int total = g.N * ceil_div(g.H * g.W, G1_KC);
-    int splits = ceil_div(3 * sm_count_1x1(), out_tiles);
+    int splits = ceil_div(3 * sm_count(), out_tiles);
     if (splits > total) splits = total;
     if (splits < 1) splits = 1;
     const int per = ceil_div(total, splits);

@@ -5,13 +5,15 @@
 // still contribute |0 - w|, exactly as F.unfold presents them to the reference kernel.
 //
 // Work decomposition.  A CTA owns TM = CG*RM output channels and a pixel tile of TI images x TH
-// output rows x the full output width.  The pixel tile is cut into row segments of RW consecutive
-// output pixels; a thread owns one segment and RM channels, i.e. an RM x RW register tile.  Input
-// channels are streamed in chunks of CK through a double-buffered shared-memory stage holding
-// the haloed input patch [CK][TI*IN_ROWS][PITCH] and the weight slab [CK*KS*KS][TM+4] (channel
-// innermost, so a thread's RM weights are two 128-bit loads that the whole warp shares).  For
-// each (ci, kh) a thread loads the (RW-1)*S+KS input values its segment touches once and slides
-// the KS taps over them in registers: two FP32 instructions per |x-w| term (subtract, add-abs).
+// output rows x SPR row segments of RW consecutive output pixels; a thread owns one segment and RM
+// channels, i.e. an RM x RW register tile (8x8, 8x4, 4x4 or 7x8 pixels x channels, chosen by the
+// launcher from the layer size).  Input channels are streamed in chunks of CK through a
+// double-buffered shared-memory stage holding the haloed input patch [CK][TI*IN_ROWS][PITCH] and the
+// weight slab [CK*KS*KS][TM+4] (channel innermost, so a thread's RM weights are 128-bit loads that
+// the whole warp shares).  For each (ci, kh) a thread loads the (RW-1)*S+KS input values its segment
+// touches once (128-/64-bit loads) and slides the KS taps over them in registers.  Per pair of
+// channels one packed add.f32x2 forms both differences and two scalar adds accumulate |d|:
+// 1.5 issue slots and 2 FP32-pipe slots per |x-w| term.
 #ifndef ADDER_FWD_PACKED
 #define ADDER_FWD_PACKED 1
 #endif
@@ -165,12 +167,6 @@ __global__ void __launch_bounds__(256, 2) adder_fwd_kernel(const FwdArgs a) {
 // ------------------------------------------------------------------------------------------
 // host side: tile plan + launch
 // ------------------------------------------------------------------------------------------
-
-static int largest_divisor_le(int n, int limit) {
-    for (int d = limit < n ? limit : n; d >= 1; --d)
-        if (n % d == 0) return d;
-    return 1;
-}
 
 // Smallest row pitch >= cols for which the 32 lanes of a warp (consecutive segments) read
 // distinct shared-memory banks as often as possible; the cost is the worst bank multiplicity.

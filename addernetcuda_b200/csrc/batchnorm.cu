@@ -252,9 +252,7 @@ static int bn_geom(int n, int c, int hw, BnGeom* g) {
     if (n <= 0 || c <= 0 || hw <= 0) return ADDER_ERR_BAD_SHAPE;
     if ((long long)n * c * hw > 2147483647LL || c > 65535) return ADDER_ERR_UNSUPPORTED;
     g->N = n; g->C = c; g->HW = hw; g->M = n * hw;
-    int dev = 0, sms = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (sms <= 0) sms = 148;
+    const int sms = sm_count();
     // about 4 CTAs per SM in total, at least 4096 elements per CTA, at most 64 slices per channel
     int splits = ceil_div(4 * sms, c);
     const int max_by_work = g->M / 4096 > 0 ? g->M / 4096 : 1;

@@ -128,4 +128,19 @@ __host__ __device__ __forceinline__ int floor_div(int a, int b) {
     return (a % b != 0 && (a < 0)) ? q - 1 : q;
 }
 
+// ---- host-side helpers shared by the tile planners -------------------------------------------------
+inline int largest_divisor_le(int n, int limit) {
+    for (int d = limit < n ? limit : n; d >= 1; --d)
+        if (n % d == 0) return d;
+    return 1;
+}
+
+// SM count of the current device (148 when no device is visible, e.g. when only planning on a CPU box).
+inline int sm_count() {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return 148;
+    return sms;
+}
+
 }  // namespace adder
