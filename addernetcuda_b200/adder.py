@@ -18,18 +18,9 @@ from . import adder_cuda
 
 # Global switch for the one-instruction clamp in the input gradient (see adder_b200.h).
 FAST_CLAMP = False
-# Run the weight gradient of a layer on a side stream, concurrently with its input gradient.
+# Run the weight gradient of a layer on a side stream, concurrently with its input gradient
+# (see adder_cuda.backward).
 OVERLAP_BACKWARD = True
-
-_side_streams: dict = {}
-
-
-def _side_stream(device):
-    s = _side_streams.get(device.index)
-    if s is None:
-        s = torch.cuda.Stream(device=device)
-        _side_streams[device.index] = s
-    return s
 
 
 class _Adder2dNCHW(Function):
@@ -52,18 +43,9 @@ class _Adder2dNCHW(Function):
         x, w = ctx.saved_tensors
         grad_out = grad_out.contiguous()
         gx = gw = None
-        if ctx.needs_input_grad[0] and ctx.needs_input_grad[1] and OVERLAP_BACKWARD:
-            # The two gradients are independent: the weight gradient goes to a side stream so that its
-            # kernels fill the SMs the input-gradient kernel leaves idle in its last wave (and vice versa).
-            # Under CUDA-graph capture this becomes two parallel branches of the graph.
-            cur = torch.cuda.current_stream(x.device)
-            side = _side_stream(x.device)
-            gw = ctx.grad_slot if ctx.grad_slot is not None else torch.empty_like(w)
-            side.wait_stream(cur)
-            with torch.cuda.stream(side):
-                adder_cuda.backward_weight(grad_out, x, w, ctx.stride, ctx.padding, adder_cuda.ETA, out=gw)
-            gx = adder_cuda.backward_input(grad_out, x, w, ctx.stride, ctx.padding, FAST_CLAMP)
-            cur.wait_stream(side)
+        if ctx.needs_input_grad[0] and ctx.needs_input_grad[1]:
+            gx, gw = adder_cuda.backward(grad_out, x, w, ctx.stride, ctx.padding, adder_cuda.ETA, FAST_CLAMP,
+                                         out_w=ctx.grad_slot, overlap=OVERLAP_BACKWARD)
             return gx, gw, None, None
         if ctx.needs_input_grad[0]:
             gx = adder_cuda.backward_input(grad_out, x, w, ctx.stride, ctx.padding, FAST_CLAMP)

@@ -132,11 +132,38 @@ def backward_weight(grad_out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, st
     return (out, norm) if return_norm else out
 
 
+_side_streams: dict = {}
+
+
+def _side_stream(dev: torch.device) -> torch.cuda.Stream:
+    s = _side_streams.get(dev.index)
+    if s is None:
+        s = torch.cuda.Stream(device=dev)
+        _side_streams[dev.index] = s
+    return s
+
+
 def backward(grad_out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stride: int = 1, padding: int = 0,
-             eta: float = ETA, fast_clamp: bool = False):
-    """(grad_x, grad_w rescaled): what adder.backward returns (adder.py:62-80), on NCHW tensors."""
-    return (backward_input(grad_out, x, w, stride, padding, fast_clamp),
-            backward_weight(grad_out, x, w, stride, padding, eta))
+             eta: float = ETA, fast_clamp: bool = False, out_w: torch.Tensor | None = None, overlap: bool = True):
+    """(grad_x, grad_w rescaled): what adder.backward returns (adder.py:62-80), on NCHW tensors.
+
+    The two gradients are independent.  With `overlap` the weight gradient is enqueued on a side stream
+    and the input gradient on the current one, and the current stream then waits for the side stream:
+    the kernels fill each other's idle SMs (first and last waves), and under CUDA-graph capture they
+    become two parallel branches of the graph.  Results are identical either way."""
+    if not overlap:
+        return (backward_input(grad_out, x, w, stride, padding, fast_clamp),
+                backward_weight(grad_out, x, w, stride, padding, eta, out=out_w))
+    dev = x.device
+    cur = torch.cuda.current_stream(dev)
+    side = _side_stream(dev)
+    gw = out_w if out_w is not None else torch.empty_like(w)
+    side.wait_stream(cur)
+    with torch.cuda.stream(side):
+        backward_weight(grad_out, x, w, stride, padding, eta, out=gw)
+    gx = backward_input(grad_out, x, w, stride, padding, fast_clamp)
+    cur.wait_stream(side)
+    return gx, gw
 
 
 def _expect_grad_shape(grad_out, g):

@@ -54,8 +54,11 @@ def main():
     peak = 2 * 128 * sms * 1.965e9
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     total = 0.0
+    times = {}
+    ops["bwd"] = lambda: ac.backward(g, x, w, s, p, fast_clamp=fast)   # both gradients, weight gradient on a side stream
     for i, (name, f) in enumerate(ops.items()):
-        print(_lib.describe_plan(i, n, ci, h, h, co, k, s, p, 1 if fast else 0))
+        if i < 3:
+            print(_lib.describe_plan(i, n, ci, h, h, co, k, s, p, 1 if fast else 0))
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -74,8 +77,14 @@ def main():
             torch.cuda.synchronize()
             ts.append(e0.elapsed_time(e1) / 4)
         ms = statistics.median(ts)
+        times[name] = ms
+        if name == "bwd":
+            break
         total += ms
         print(f"  {name:8s} {ms * 1e3:9.1f} us   {3 * T / ms / 1e6:9.0f} Gop/s   {100 * 3 * T / (ms * 1e-3) / peak:5.1f} % of FP32 peak")
+    both = times["forward"] + times["bwd"]
+    print(f"  bwd (grad_w beside grad_x) {times['bwd'] * 1e3:9.1f} us;  forward + that: {both * 1e3:9.1f} us   "
+          f"{9 * T / both / 1e6:9.0f} Gop/s   {100 * 9 * T / (both * 1e-3) / peak:5.1f} % of FP32 peak")
     print(f"  fwd+bwd  {total * 1e3:9.1f} us   {9 * T / total / 1e6:9.0f} Gop/s   {100 * 9 * T / (total * 1e-3) / peak:5.1f} % of FP32 peak")
 
 

@@ -178,8 +178,9 @@ def run_reference_arm(args):
 # ------------------------------------------------------------------------------------------ GPU arm
 
 def time_layer_ops(n, shape, iters=5, inner=4):
-    """Device time (ms) of the three adder kernels of one layer, CUDA events on the current stream
-    around a CUDA-graph replay of `inner` launches, L2 flushed before every replay."""
+    """Device time (ms) of the three adder kernels of one layer, and of the two gradient kernels issued
+    together as the layer's backward does, CUDA events on the current stream around a CUDA-graph
+    replay of `inner` launches, L2 flushed before every replay."""
     import torch
     from addernetcuda_b200 import adder_cuda as ac
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -192,7 +193,9 @@ def time_layer_ops(n, shape, iters=5, inner=4):
     out = {}
     ops = {"fwd": lambda: ac.forward(x, wt, s, p),
            "grad_x": lambda: ac.backward_input(g, x, wt, s, p, fast_clamp=True),
-           "grad_w": lambda: ac.backward_weight(g, x, wt, s, p)}
+           "grad_w": lambda: ac.backward_weight(g, x, wt, s, p),
+           # both gradients the way the layer's backward issues them: weight gradient on a side stream
+           "bwd": lambda: ac.backward(g, x, wt, s, p, fast_clamp=True)}
     for name, f in ops.items():
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -340,7 +343,7 @@ def run_gpu_arm(args):
         f_max = (clocks or {}).get("sm_max_mhz") or peaks.get("sm_max_mhz") or 1965.0
         fp32_peak = 2 * 128 * sms * f_max * 1e6            # FLOP/s of the FP32 CUDA cores (FMA = 2)
         hbm_peak = peaks.get("hbm_gbs", 6650.0)
-        tot = {"fwd": 0.0, "grad_x": 0.0, "grad_w": 0.0}
+        tot = {"fwd": 0.0, "grad_x": 0.0, "grad_w": 0.0, "bwd": 0.0}
         tot_T = 0.0
         per_layer = []
         for shp, mult in RESNET20_LAYERS:
@@ -349,10 +352,11 @@ def run_gpu_arm(args):
             tot_T += T * mult
             for k in tot:
                 tot[k] += t[k] * mult
-        dom = max(tot, key=tot.get)
+        dom = max(("fwd", "grad_x", "grad_w"), key=tot.get)
         dom_kernel = {"fwd": "adder_fwd_kernel", "grad_x": "adder_gx_kernel", "grad_w": "adder_gw_kernel"}[dom]
         achieved = 3 * tot_T / (tot[dom] * 1e-3)
-        all_ms = sum(tot.values())
+        all_ms = tot["fwd"] + tot["grad_x"] + tot["grad_w"]
+        pass_ms = tot["fwd"] + tot["bwd"]
         # algorithmic bytes of the dominant kernel over the layer set (inputs + outputs once)
         line["roofline"] = {
             "bound": "fp32", "kernel": dom_kernel,
@@ -368,7 +372,9 @@ def run_gpu_arm(args):
             "workload": "the 20 adder layers of ResNet-20 at batch 256, kernels timed alone (L2 flushed)",
             "fwd_ms": tot["fwd"], "grad_x_ms": tot["grad_x"], "grad_w_ms": tot["grad_w"],
             "fwd_bwd_gops": 9 * tot_T / (all_ms * 1e-3) / 1e9, "pct_fp32_peak": 100 * 9 * tot_T / (all_ms * 1e-3) / fp32_peak,
-            "share_of_step": all_ms / (ms_total / K),
+            "bwd_ms": tot["bwd"], "bwd_note": "both gradient kernels issued as the layer's backward does (weight gradient on a side stream)",
+            "pass_gops": 9 * tot_T / (pass_ms * 1e-3) / 1e9, "pass_pct_fp32_peak": 100 * 9 * tot_T / (pass_ms * 1e-3) / fp32_peak,
+            "share_of_step": pass_ms / (ms_total / K),
         }
         sweep = []
         for shp in SWEEP_SHAPES:
@@ -378,7 +384,8 @@ def run_gpu_arm(args):
             ci, co, h, w, s, k, p = shp
             x_b, w_b, o_b = 256 * ci * h * w * 4, co * ci * k * k * 4, T // (ci * k * k) * 4
             sweep.append({"shape": {"ci": ci, "co": co, "h": h, "w": w, "stride": s, "k": k}, "fwd_ms": t["fwd"],
-                          "grad_x_ms": t["grad_x"], "grad_w_ms": t["grad_w"],
+                          "grad_x_ms": t["grad_x"], "grad_w_ms": t["grad_w"], "bwd_ms": t["bwd"],
+                          "pass_pct_fp32_peak": 100 * 9 * T / ((t["fwd"] + t["bwd"]) * 1e-3) / fp32_peak,
                           "fwd_bwd_gops": 9 * T / (ms * 1e-3) / 1e9, "pct_fp32_peak": 100 * 9 * T / (ms * 1e-3) / fp32_peak,
                           "fwd_gbs": (x_b + w_b + o_b) / (t["fwd"] * 1e-3) / 1e9})
         line["layers"] = sweep
