@@ -39,7 +39,10 @@ __global__ void __launch_bounds__(256, GW_MIN_BLOCKS) adder_gw_kernel(const GwAr
 
     const int tid = threadIdx.x;
     const int nthreads = blockDim.x;
-    const int split = blockIdx.x;
+    // Pixel tiles are dealt out as evenly as they go: the first `tiles_rem` ranges hold one tile more.
+    // Which CTA of a row takes which range is rotated from one output tile (blockIdx.y) to the next, so
+    // that the CTAs that share an SM (linear CTA ids one wave apart) do not all hold a long range.
+    const int split = (int)((blockIdx.x + (unsigned)a.splits - (blockIdx.y * (unsigned)a.tiles_rem) % (unsigned)a.splits) % (unsigned)a.splits);
     uint32_t ct_o, ct_c;
     a.d_ci_tiles.divmod(blockIdx.y, ct_o, ct_c);
     const int co0 = ct_o * a.TM, ci0 = ct_c * a.TCI;
@@ -61,9 +64,8 @@ __global__ void __launch_bounds__(256, GW_MIN_BLOCKS) adder_gw_kernel(const GwAr
             for (int t = 0; t < KK; ++t) acc[m][c][t] = 0.f;
     }
 
-    const int t_begin = split * a.tiles_per_split;
-    int t_end = t_begin + a.tiles_per_split;
-    if (t_end > a.tiles_total) t_end = a.tiles_total;
+    const int t_begin = split * a.tiles_per_split + min(split, a.tiles_rem);
+    const int t_end = t_begin + a.tiles_per_split + (split < a.tiles_rem ? 1 : 0);
 
     auto fill = [&](int tile, int stage) {
         uint32_t tn, th, tw, tnh;
@@ -416,10 +418,9 @@ static GwPlan plan_gw_t(const Geom& g, const TileHint& hint) {
     int splits = ceil_div(target_ctas, out_tiles);
     if (splits > a.tiles_total) splits = a.tiles_total;
     if (splits < 1) splits = 1;
-    a.tiles_per_split = ceil_div(a.tiles_total, splits);
-    if (a.tiles_per_split < 1) a.tiles_per_split = 1;
-    a.splits = ceil_div(a.tiles_total, a.tiles_per_split);
-    if (a.splits < 1) a.splits = 1;
+    a.splits = splits;
+    a.tiles_per_split = a.tiles_total / splits;      // the first tiles_rem ranges hold one more
+    a.tiles_rem = a.tiles_total % splits;
     px.d_cols = FastDiv(px.COLS); px.d_rows = FastDiv(px.ROWS);
     pg.d_cols = FastDiv(pg.COLS); pg.d_rows = FastDiv(pg.ROWS);
     a.d_tiles_h = FastDiv(a.tiles_h);
@@ -463,9 +464,9 @@ int describe_gw(const Geom& g, const TileHint& hint, char* buf, size_t n) {
     const GwArgs& a = p.a;
     snprintf(buf, n,
              "gw k=%d s=%d CGO=%d CGC=%d TM=%d TCI=%d PL=%d TI=%d TH=%d SPR=%d SEGS=%d xrows=%d xcols=%d xpitch=%d gpitch=%d "
-             "threads=%d smem=%zu tiles=%d splits=%d tiles_per_split=%d out_tiles=%d fin_blocks=%d gemm1x1=%d status=%d",
+             "threads=%d smem=%zu tiles=%d splits=%d tiles_per_split=%d+%d/%d out_tiles=%d fin_blocks=%d gemm1x1=%d status=%d",
              g.k, g.stride, a.CGO, a.CGC, a.TM, a.TCI, a.PL, a.TI, a.TH, a.SPR, a.SEGS, a.pdx.ROWS, a.pdx.COLS, a.pdx.PITCH,
-             a.pdg.PITCH, p.threads, p.smem, a.tiles_total, a.splits, a.tiles_per_split,
+             a.pdg.PITCH, p.threads, p.smem, a.tiles_total, a.splits, a.tiles_per_split, a.tiles_rem, a.splits,
              ceil_div(g.Co, a.TM) * a.n_ci_tiles, p.fin_blocks, (int)p.use_1x1, p.status);
     return ADDER_OK;
 }

@@ -57,7 +57,7 @@ struct GwArgs {
     int CGO, CGC, TM, TCI;        // output tile: TM = CGO*RM channels out, TCI = CGC*RC channels in
     int PL;                       // pixel lanes: threads that share one output tile and split the segments
     int XCH_STRIDE, GCH_STRIDE;
-    int xs_stage, gs_stage, tiles_h, tiles_w, tiles_total, splits, tiles_per_split, n_ci_tiles;
+    int xs_stage, gs_stage, tiles_h, tiles_w, tiles_total, splits, tiles_per_split, tiles_rem, n_ci_tiles;
     FastDiv d_tiles_h, d_tiles_w, d_spr, d_th, d_pl, d_cgo, d_ci_tiles;
 };
 
