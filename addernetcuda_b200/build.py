@@ -18,7 +18,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 INCLUDE = PKG.parent / "include"
 LIB = PKG / "libadder_b200.so"
-SOURCES = ["api.cu", "adder_fwd.cu", "adder_bwd_input.cu", "adder_bwd_weight.cu", "adder_bwd_weight_1x1.cu", "static_scratch.cu", "batchnorm.cu"]
+SOURCES = ["api.cu", "adder_fwd.cu", "adder_bwd_input.cu", "adder_bwd_weight.cu", "adder_bwd_weight_1x1.cu", "adder_pointwise.cu", "static_scratch.cu", "batchnorm.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -495,6 +495,11 @@ static int choose_gx_rw(const Geom& g, const TileHint& hint) {
     else { if (fast) { CALL(KS_, S_, 8, 4, true) } else { CALL(KS_, S_, 8, 4, false) } }
 
 int describe_gx(const Geom& g, int fast, const TileHint& hint, char* buf, size_t n) {
+    if (hint.is_default() && pointwise_applicable(g)) {
+        snprintf(buf, n, "gx k=1 s=%d pointwise fast=%d: one thread per output position, 16 input channels per CTA, threads=256 "
+                 "grid=(%d,%d) status=0", g.stride, fast, ceil_div(g.N * g.Ho * g.Wo, 256), ceil_div(g.Ci, 16));
+        return ADDER_OK;
+    }
     const int rw = choose_gx_rw(g, hint);
     GxPlan p;
     int st = ADDER_ERR_UNSUPPORTED;
@@ -512,6 +517,7 @@ int describe_gx(const Geom& g, int fast, const TileHint& hint, char* buf, size_t
 
 int launch_gx(const Geom& g, const float* gout, const float* x, const float* w, float* gx, int fast,
               int accumulate, const TileHint& hint, cudaStream_t stream) {
+    if (hint.is_default() && pointwise_applicable(g)) return launch_pointwise_gx(g, gout, x, w, gx, fast, accumulate, stream);
     const int rw = choose_gx_rw(g, hint);
 #define ADDER_GX_LAUNCH(KS_, S_, RW_, RC_, FAST_) \
     return launch_gx_t<KS_, S_, RW_, RC_, FAST_>(g, gout, x, w, gx, accumulate, hint, stream);

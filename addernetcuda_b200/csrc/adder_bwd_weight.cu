@@ -324,6 +324,7 @@ struct GwPlan {
     int fin_blocks;
     int status;
     bool use_1x1 = false;   // 1x1 stride-1 layers with enough channels take the GEMM-style kernel
+    bool use_pointwise = false;   // 1x1 stride-2 layers with few channels: adder_pointwise.cu
 };
 
 template <int KS, int S, int RW, int RM, int RC>
@@ -442,6 +443,10 @@ static GwPlan plan_gw(const Geom& g, const TileHint& hint) {
         p.use_1x1 = true;
         p.a.splits = gw1x1_splits(g);
     }
+    if (p.status == ADDER_OK && pointwise_applicable(g) && hint.is_default()) {
+        p.use_pointwise = true;
+        p.a.splits = pointwise_gw_splits(g);
+    }
     return p;
 }
 
@@ -464,10 +469,10 @@ int describe_gw(const Geom& g, const TileHint& hint, char* buf, size_t n) {
     const GwArgs& a = p.a;
     snprintf(buf, n,
              "gw k=%d s=%d CGO=%d CGC=%d TM=%d TCI=%d PL=%d TI=%d TH=%d SPR=%d SEGS=%d xrows=%d xcols=%d xpitch=%d gpitch=%d "
-             "threads=%d smem=%zu tiles=%d splits=%d tiles_per_split=%d+%d/%d out_tiles=%d fin_blocks=%d gemm1x1=%d status=%d",
+             "threads=%d smem=%zu tiles=%d splits=%d tiles_per_split=%d+%d/%d out_tiles=%d fin_blocks=%d gemm1x1=%d pointwise=%d status=%d",
              g.k, g.stride, a.CGO, a.CGC, a.TM, a.TCI, a.PL, a.TI, a.TH, a.SPR, a.SEGS, a.pdx.ROWS, a.pdx.COLS, a.pdx.PITCH,
              a.pdg.PITCH, p.threads, p.smem, a.tiles_total, a.splits, a.tiles_per_split, a.tiles_rem, a.splits,
-             ceil_div(g.Co, a.TM) * a.n_ci_tiles, p.fin_blocks, (int)p.use_1x1, p.status);
+             ceil_div(g.Co, a.TM) * a.n_ci_tiles, p.fin_blocks, (int)p.use_1x1, (int)p.use_pointwise, p.status);
     return ADDER_OK;
 }
 
@@ -509,7 +514,8 @@ int launch_gw(const Geom& g, const float* gout, const float* x, const float* w, 
 
     const bool rw7 = (g.Wo % 8 != 0) && (g.Wo % 7 == 0);
     int st = ADDER_ERR_UNSUPPORTED;
-    if (p.use_1x1) st = launch_gw1x1(g, gout, x, p.a.part, p.a.gsum_part, ticket, p.a.splits, stream);
+    if (p.use_pointwise) st = launch_pointwise_gw(g, gout, x, p.a.part, p.a.gsum_part, ticket, p.a.splits, stream);
+    else if (p.use_1x1) st = launch_gw1x1(g, gout, x, p.a.part, p.a.gsum_part, ticket, p.a.splits, stream);
     else if (g.k == 3 && g.stride == 1) st = rw7 ? launch_main_t<3, 1, 7, 4, 2>(p, stream) : launch_main_t<3, 1, 8, 4, 2>(p, stream);
     else if (g.k == 3 && g.stride == 2) st = rw7 ? launch_main_t<3, 2, 7, 4, 2>(p, stream) : launch_main_t<3, 2, 8, 4, 2>(p, stream);
     else if (g.k == 1 && g.stride == 1) st = rw7 ? launch_main_t<1, 1, 7, 8, 4>(p, stream) : launch_main_t<1, 1, 8, 8, 4>(p, stream);

@@ -329,6 +329,11 @@ static void choose_fwd_tile(const Geom& g, const TileHint& hint, int& rw, int& r
     else if (rw == 4 && rm == 4) { CALL(KS_, S_, 4, 4) }
 
 int describe_fwd(const Geom& g, const TileHint& hint, char* buf, size_t n) {
+    if (hint.is_default() && pointwise_applicable(g)) {
+        snprintf(buf, n, "fwd k=1 s=%d pointwise: one thread per output position, 16 output channels per CTA, threads=256 "
+                 "grid=(%d,%d) status=0", g.stride, ceil_div(g.N * g.Ho * g.Wo, 256), ceil_div(g.Co, 16));
+        return ADDER_OK;
+    }
     int rw = 8, rm = 8;
     choose_fwd_tile(g, hint, rw, rm);
     FwdPlan p;
@@ -347,6 +352,7 @@ int describe_fwd(const Geom& g, const TileHint& hint, char* buf, size_t n) {
 
 int launch_fwd(const Geom& g, const float* x, const float* w, float* out, const TileHint& hint,
                cudaStream_t stream) {
+    if (hint.is_default() && pointwise_applicable(g)) return launch_pointwise_fwd(g, x, w, out, stream);
     int rw = 8, rm = 8;
     choose_fwd_tile(g, hint, rw, rm);
 #define ADDER_FWD_LAUNCH(KS_, S_, RW_, RM_) return launch_fwd_t<KS_, S_, RW_, RM_>(g, x, w, out, hint, stream);

@@ -18,6 +18,7 @@ struct TileHint {
     int smem_kb = 0;   // shared-memory budget per CTA
     int rw = 0;        // pixels per thread segment (register tile width)
     int rm = 0;        // channels per thread (register tile height)
+    bool is_default() const { return !(threads | cg | th | ti | ck | smem_kb | rw | rm); }
 };
 
 struct FwdArgs {
@@ -79,6 +80,16 @@ size_t gw_workspace_bytes(const Geom& g, const TileHint& hint);
 int launch_gw(const Geom& g, const float* gout, const float* x, const float* w, float* gw, float eta,
               float* out_norm, int accumulate, void* workspace, size_t workspace_bytes, const TileHint& hint,
               cudaStream_t s);
+
+// 1x1 stride-2 layers with at most 64 channels: one thread per output position (adder_pointwise.cu).
+// Chosen automatically unless a tile hint asks for the tiled kernels.
+bool pointwise_applicable(const Geom& g);
+int launch_pointwise_fwd(const Geom& g, const float* x, const float* w, float* out, cudaStream_t stream);
+int launch_pointwise_gx(const Geom& g, const float* gout, const float* x, const float* w, float* gx, int fast,
+                        int accumulate, cudaStream_t stream);
+int pointwise_gw_splits(const Geom& g);
+int launch_pointwise_gw(const Geom& g, const float* gout, const float* x, float* part, float* gsum_part,
+                        unsigned int* ticket, int splits, cudaStream_t stream);
 
 bool gw1x1_applicable(const Geom& g);
 int gw1x1_splits(const Geom& g);

@@ -124,6 +124,7 @@ def test_every_register_tile(name, tile, golden, ac):
     finally:
         lib.adder_b200_set_micro_tile(0, 0, 0)
         lib.adder_b200_set_micro_tile(1, 0, 0)
+        lib.adder_b200_set_tile_hint(2, 0, 0, 0, 0, 0, 0)
 
 
 def test_module_autograd_and_bias(ac):
@@ -208,3 +209,65 @@ def test_errors_are_statuses_not_aborts(ac):
     ac.ADDER_CONV(torch.randn(27, 50, device=DEV), torch.randn(5, 27, device=DEV), y)
     assert torch.isfinite(y).all()
     assert ac.forward(torch.zeros(0, 3, 8, 8, device=DEV), torch.randn(4, 3, 3, 3, device=DEV), 1, 1).shape == (0, 4, 8, 8)
+
+
+@pytest.mark.parametrize("geom", [(3, 16, 32, 32, 32), (2, 32, 64, 16, 16), (2, 5, 7, 9, 11), (1, 33, 20, 6, 5), (2, 64, 64, 8, 8)],
+                         ids=lambda t: "n%d_c%dto%d_%dx%d" % t)
+def test_pointwise_stride2_kernels(geom, ac):
+    """1x1 stride-2 layers with few channels take the one-thread-per-position kernels.  They must agree
+    with the float64 oracle, write every input pixel (zeros where no output reads), honour the
+    accumulate flag, and agree with the tiled kernels that a tile hint selects instead."""
+    from addernetcuda_b200 import _lib
+    lib = _lib.load()
+    n, ci, co, h, w_ = geom
+    assert "pointwise" in _lib.describe_plan(0, n, ci, h, w_, co, 1, 2, 0, 0)
+    assert "pointwise" in _lib.describe_plan(1, n, ci, h, w_, co, 1, 2, 0, 1)
+    gen = torch.Generator().manual_seed(77 + n + ci + co + h)
+    x = torch.randn(n, ci, h, w_, generator=gen)
+    w = torch.randn(co, ci, 1, 1, generator=gen) * 0.7
+    ho, wo = (h - 1) // 2 + 1, (w_ - 1) // 2 + 1
+    g = torch.randn(n, co, ho, wo, generator=gen)
+    want_out = O.adder2d_forward_direct(x, w, 2, 0)
+    want_gx, want_gws, want_gw = O.adder2d_backward_direct(g, x, w, 2, 0)
+    xg, wg, gg = x.to(DEV), w.to(DEV), g.to(DEV)
+    out = ac.forward(xg, wg, 2, 0)
+    _assert(O.compare("out", out, want_out))
+    assert "pointwise=1" in _lib.describe_plan(2, n, ci, h, w_, co, 1, 2, 0, 0)
+    _assert(O.compare("grad_w", ac.backward_weight(gg, xg, wg, 2, 0), want_gws))
+    gw_raw = ac.backward_weight(gg, xg, wg, 2, 0, eta=0.0)
+    scale = max(1.0, float(want_gw.abs().max()))
+    _assert(O.compare("grad_w_unscaled/scale", gw_raw.cpu() / scale, want_gw / scale))
+    for fast in (False, True):
+        gx = ac.backward_input(gg, xg, wg, 2, 0, fast_clamp=fast)
+        _assert(O.compare("grad_x fast=%d" % fast, gx, want_gx))
+        # every element is written: a poisoned buffer comes back finite, zeros off the sampled grid
+        buf = torch.full_like(xg, float("nan"))
+        flags = _lib.FLAG_FAST_CLAMP if fast else 0
+        args = (gg.data_ptr(), xg.data_ptr(), wg.data_ptr(), buf.data_ptr(), n, ci, h, w_, co, 1, 2, 0)
+        stream = torch.cuda.current_stream().cuda_stream
+        assert lib.adder_b200_backward_input(*args, flags, stream) == 0
+        assert torch.isfinite(buf).all()
+        mask = torch.zeros(h, w_, dtype=torch.bool, device=DEV)
+        mask[::2, ::2] = True
+        assert (buf[:, :, ~mask] == 0).all()
+        assert torch.equal(buf, gx)
+        # accumulate: adds on the sampled grid, leaves the rest alone
+        base = torch.randn_like(xg)
+        acc = base.clone()
+        args = args[:3] + (acc.data_ptr(),) + args[4:]
+        assert lib.adder_b200_backward_input(*args, flags | _lib.FLAG_ACCUMULATE, stream) == 0
+        _assert(O.compare("accumulated", acc, (base + gx).cpu()))
+        assert torch.equal(acc[:, :, ~mask], base[:, :, ~mask])
+    try:    # the tiled kernels on the same inputs
+        assert lib.adder_b200_set_micro_tile(0, 8, 4) == 0
+        assert lib.adder_b200_set_micro_tile(1, 4, 4) == 0
+        assert "pointwise" not in _lib.describe_plan(0, n, ci, h, w_, co, 1, 2, 0, 0)
+        _assert(O.compare("tiled out", ac.forward(xg, wg, 2, 0), out.cpu()))
+        _assert(O.compare("tiled grad_x", ac.backward_input(gg, xg, wg, 2, 0, fast_clamp=True), want_gx))
+        assert lib.adder_b200_set_tile_hint(2, 256, 0, 0, 0, 0, 0) == 0
+        assert "pointwise=0" in _lib.describe_plan(2, n, ci, h, w_, co, 1, 2, 0, 0)
+        _assert(O.compare("tiled grad_w", ac.backward_weight(gg, xg, wg, 2, 0), want_gws))
+    finally:
+        lib.adder_b200_set_micro_tile(0, 0, 0)
+        lib.adder_b200_set_micro_tile(1, 0, 0)
+        lib.adder_b200_set_tile_hint(2, 0, 0, 0, 0, 0, 0)
