@@ -22,6 +22,7 @@ _GEOM = [c_int] * 8  # n, ci, h, w, co, k, stride, pad
 SIGNATURES = {
     "adder_b200_status_string": (c_char_p, [c_int]),
     "adder_b200_version": (c_int, []),
+    "adder_b200_launch_count": (ctypes.c_ulonglong, []),
     "adder_b200_output_size": (c_int, [c_int, c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)]),
     "adder_b200_forward": (c_int, [c_void_p, c_void_p, c_void_p, *_GEOM, c_void_p]),
     "adder_b200_backward_input": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, *_GEOM, c_int, c_void_p]),

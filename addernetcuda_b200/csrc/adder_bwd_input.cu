@@ -471,7 +471,7 @@ static int launch_gx_t(const Geom& g, const float* gout, const float* x, const f
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem) != cudaSuccess)
         return ADDER_ERR_CUDA;
     kern<<<dim3((unsigned)p.gx, (unsigned)p.gy), p.threads, p.smem, stream>>>(p.a);
-    return cudaGetLastError() == cudaSuccess ? ADDER_OK : ADDER_ERR_CUDA;
+    return launched();
 }
 
 // Register tile: 4 input channels x RW pixels.  8-pixel segments unless the layer is too small to fill

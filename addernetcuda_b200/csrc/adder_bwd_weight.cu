@@ -492,7 +492,7 @@ static int launch_main_t(const GwPlan& p, cudaStream_t stream) {
         return ADDER_ERR_CUDA;
     const int out_tiles = ceil_div(p.a.g.Co, p.a.TM) * p.a.n_ci_tiles;
     kern<<<dim3((unsigned)p.a.splits, (unsigned)out_tiles), p.threads, p.smem, stream>>>(p.a);
-    return cudaGetLastError() == cudaSuccess ? ADDER_OK : ADDER_ERR_CUDA;
+    return launched();
 }
 
 int launch_gw(const Geom& g, const float* gout, const float* x, const float* w, float* gw, float eta,
@@ -529,17 +529,17 @@ int launch_gw(const Geom& g, const float* gout, const float* x, const float* w, 
     const bool need_norm = eta > 0.f || out_norm != nullptr;
     if (need_norm && CoK <= (size_t)FUSED_FINISH_MAX) {
         adder_gw_finish_kernel<<<p.fin_blocks, FIN_THREADS, 0, stream>>>(f, p.fin_blocks, ticket);
-        return cudaGetLastError() == cudaSuccess ? ADDER_OK : ADDER_ERR_CUDA;
+        return launched();
     }
     adder_gw_reduce_kernel<<<p.fin_blocks, FIN_THREADS, 0, stream>>>(f);
-    if (cudaGetLastError() != cudaSuccess) return ADDER_ERR_CUDA;
+    if (launched() != ADDER_OK) return ADDER_ERR_CUDA;
     if (need_norm) {
         float* scale = norm_part + p.fin_blocks;
         adder_gw_norm_kernel<<<1, 1024, 0, stream>>>(f, p.fin_blocks, scale);
-        if (cudaGetLastError() != cudaSuccess) return ADDER_ERR_CUDA;
+        if (launched() != ADDER_OK) return ADDER_ERR_CUDA;
         if (eta > 0.f) {
             adder_gw_scale_kernel<<<ceil_div((int)CoK, FIN_THREADS), FIN_THREADS, 0, stream>>>(gw, (int)CoK, scale);
-            if (cudaGetLastError() != cudaSuccess) return ADDER_ERR_CUDA;
+            if (launched() != ADDER_OK) return ADDER_ERR_CUDA;
         }
     }
     return ADDER_OK;

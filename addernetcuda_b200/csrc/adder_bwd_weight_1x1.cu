@@ -177,7 +177,7 @@ int launch_gw1x1(const Geom& g, const float* gout, const float* x, float* part, 
             return ADDER_ERR_CUDA;
         adder_gw1x1_kernel<false><<<grid, G1_THREADS, smem, stream>>>(a);
     }
-    return cudaGetLastError() == cudaSuccess ? ADDER_OK : ADDER_ERR_CUDA;
+    return launched();
 }
 
 }  // namespace adder

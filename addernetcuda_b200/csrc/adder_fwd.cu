@@ -296,7 +296,7 @@ static int launch_fwd_t(const Geom& g, const float* x, const float* w, float* ou
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
     if (e != cudaSuccess) return ADDER_ERR_CUDA;
     kern<<<dim3((unsigned)p.gx, (unsigned)p.gy), p.threads, p.smem, stream>>>(p.a);
-    return cudaGetLastError() == cudaSuccess ? ADDER_OK : ADDER_ERR_CUDA;
+    return launched();
 }
 
 // Register tile (pixels x channels per thread).  The widest tile has the fewest shared-memory loads

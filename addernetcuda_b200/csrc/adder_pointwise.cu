@@ -158,7 +158,7 @@ int launch_pointwise_fwd(const Geom& g, const float* x, const float* w, float* o
     if (g.Ci <= 16) adder_pw_fwd_kernel<16><<<grid, PW_THREADS, 0, stream>>>(a);
     else if (g.Ci <= 32) adder_pw_fwd_kernel<32><<<grid, PW_THREADS, 0, stream>>>(a);
     else adder_pw_fwd_kernel<64><<<grid, PW_THREADS, 0, stream>>>(a);
-    return cudaGetLastError() == cudaSuccess ? ADDER_OK : ADDER_ERR_CUDA;
+    return launched();
 }
 
 int launch_pointwise_gx(const Geom& g, const float* gout, const float* x, const float* w, float* gx, int fast,
@@ -172,7 +172,7 @@ int launch_pointwise_gx(const Geom& g, const float* gout, const float* x, const 
     const size_t smem = (size_t)g.Co * PW_CT * sizeof(float);
     if (fast) adder_pw_gx_kernel<true><<<grid, PW_THREADS, smem, stream>>>(a);
     else adder_pw_gx_kernel<false><<<grid, PW_THREADS, smem, stream>>>(a);
-    return cudaGetLastError() == cudaSuccess ? ADDER_OK : ADDER_ERR_CUDA;
+    return launched();
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -337,7 +337,7 @@ int launch_pointwise_gw(const Geom& g, const float* gout, const float* x, float*
     if (cudaFuncSetAttribute(adder_pw_gw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return ADDER_ERR_CUDA;
     adder_pw_gw_kernel<<<splits, PW_THREADS, smem, stream>>>(a);
-    return cudaGetLastError() == cudaSuccess ? ADDER_OK : ADDER_ERR_CUDA;
+    return launched();
 }
 
 }  // namespace adder

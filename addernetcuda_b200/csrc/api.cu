@@ -22,6 +22,8 @@ struct HintSlot {
     }
 };
 HintSlot g_hints[3];
+std::atomic<unsigned long long> g_launches{0};
+
 
 // Validates a layer geometry and fills Geom.  Every tensor must have fewer than 2^31 elements
 // (the kernels index tiles with 32-bit integers and element offsets with 64-bit ones).
@@ -47,6 +49,10 @@ int make_col_geom(int K, int P, int Co, Geom* g) {
 
 }  // namespace
 
+namespace adder {
+void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
+}  // namespace adder
+
 extern "C" {
 
 const char* adder_b200_status_string(int status) {
@@ -65,6 +71,8 @@ const char* adder_b200_status_string(int status) {
 }
 
 int adder_b200_version(void) { return ADDER_B200_VERSION; }
+
+unsigned long long adder_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int adder_b200_output_size(int h, int w, int k, int stride, int pad, int* ho, int* wo) {
     if (ho == nullptr || wo == nullptr) return ADDER_ERR_NULL_POINTER;

@@ -298,7 +298,7 @@ int adder_b200_batchnorm_forward(const float* y, const float* gamma, const float
     BnFwdArgs a{y, gamma, beta, residual, z, save_mean, save_invstd, running_mean, running_var, num_batches_tracked,
                 part, eps, momentum, relu};
     bn_apply_kernel<<<grid, BN_THREADS, 0, s>>>(a, g);
-    return cudaGetLastError() == cudaSuccess ? ADDER_OK : ADDER_ERR_CUDA;
+    return launched(2);
 }
 
 int adder_b200_batchnorm_backward(const float* dz, const float* y, const float* z, const float* gamma,
@@ -320,7 +320,7 @@ int adder_b200_batchnorm_backward(const float* dz, const float* y, const float* 
     const dim3 grid(g.splits, c);
     bn_bwd_reduce_kernel<<<grid, BN_THREADS, 0, s>>>(a, g);
     bn_bwd_apply_kernel<<<grid, BN_THREADS, 0, s>>>(a, g);
-    return cudaGetLastError() == cudaSuccess ? ADDER_OK : ADDER_ERR_CUDA;
+    return launched(2);
 }
 
 }  // extern "C"

@@ -73,6 +73,16 @@ struct GwFinishArgs {
     float eta;
 };
 
+// Every kernel launch of the library is counted (adder_b200_launch_count): callers use it to state how
+// many of these kernels a step launched.  A relaxed atomic increment on the host; nothing on the device.
+void count_launch(int n = 1);
+// After a launch: the status of the launch, counting it when it went through.
+inline int launched(int n = 1) {
+    if (cudaGetLastError() != cudaSuccess) return ADDER_ERR_CUDA;
+    count_launch(n);
+    return ADDER_OK;
+}
+
 int launch_fwd(const Geom& g, const float* x, const float* w, float* out, const TileHint& hint, cudaStream_t s);
 int launch_gx(const Geom& g, const float* gout, const float* x, const float* w, float* gx, int fast,
               int accumulate, const TileHint& hint, cudaStream_t s);

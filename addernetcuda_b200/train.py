@@ -39,6 +39,7 @@ class TrainStep:
         self.use_graph = use_graph
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.stream = torch.cuda.Stream(device=self.device)
+        self._stage = None      # staging buffers, copy stream and events of prefetch()
 
     def _body(self, update: bool = True) -> None:
         if self.ddp is not None:
@@ -71,6 +72,30 @@ class TrainStep:
     def load_batch(self, images: torch.Tensor, labels: torch.Tensor) -> None:
         self.images.copy_(images, non_blocking=True)
         self.labels.copy_(labels, non_blocking=True)
+
+    def prefetch(self, images: torch.Tensor, labels: torch.Tensor) -> None:
+        """Start copying the NEXT batch (pinned host memory) into staging buffers on a copy stream, so
+        that the transfer overlaps the step that is running; `step_prefetched` consumes it."""
+        if self._stage is None:
+            self._stage = (torch.empty_like(self.images), torch.empty_like(self.labels))
+            self._copy_stream = torch.cuda.Stream(device=self.device)
+            self._copied = torch.cuda.Event()
+            self._consumed = torch.cuda.Event()
+            self._consumed.record(torch.cuda.current_stream(self.device))
+        self._copy_stream.wait_event(self._consumed)      # the previous batch has left the staging buffers
+        with torch.cuda.stream(self._copy_stream):
+            self._stage[0].copy_(images, non_blocking=True)
+            self._stage[1].copy_(labels, non_blocking=True)
+            self._copied.record(self._copy_stream)
+
+    def step_prefetched(self) -> torch.Tensor:
+        """Run one step on the batch last given to `prefetch`."""
+        cur = torch.cuda.current_stream(self.device)
+        cur.wait_event(self._copied)
+        self.images.copy_(self._stage[0], non_blocking=True)
+        self.labels.copy_(self._stage[1], non_blocking=True)
+        self._consumed.record(cur)
+        return self.run()
 
     def run(self) -> torch.Tensor:
         """Run one step on whatever the static buffers hold."""

@@ -293,12 +293,16 @@ def run_gpu_arm(args):
     clocks = sampler.stop() if rank == 0 else None
     final_loss = float(ts.loss)
 
-    # ---- e2e: every step copies its batch from pinned host memory and reads the loss back
+    # ---- e2e: every step copies its batch from pinned host memory (prefetched one step ahead on a copy
+    # stream, as a data loader would) and reads the loss back
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(K):
-        loss = ts.step(host_images, host_labels)
+    ts.prefetch(host_images, host_labels)
+    for i in range(K):
+        loss = ts.step_prefetched()
+        if i + 1 < K:
+            ts.prefetch(host_images, host_labels)      # the next batch's copy overlaps this step
         _ = loss.item()
     e1.record()
     barrier()
@@ -307,7 +311,13 @@ def run_gpu_arm(args):
     d2h = 4
 
     n_adder = sum(1 for m in net.modules() if isinstance(m, A.adder2d))
-    launches_per_step = n_adder * 6   # forward, input gradient, weight gradient (main, reduce, norm, scale)
+    # kernels of this library per step: counted by the library across one eager forward + backward
+    # (a graph replay runs the same kernels without passing through the host-side counter)
+    from addernetcuda_b200 import _lib
+    before = _lib.load().adder_b200_launch_count()
+    ts.forward_backward_only()
+    torch.cuda.synchronize()
+    launches_per_step = int(_lib.load().adder_b200_launch_count() - before)
 
     line = None
     if rank == 0:

@@ -60,6 +60,11 @@ ADDER_API const char* adder_b200_status_string(int status);
 /* ADDER_B200_VERSION of the loaded library. */
 ADDER_API int adder_b200_version(void);
 
+/* Number of kernels this library has launched in this process so far (a host-side counter; launches
+ * replayed from a captured CUDA graph are not seen).  No reference counterpart: a benchmark uses the
+ * difference across one eager step to state how many of these kernels a step runs. */
+ADDER_API unsigned long long adder_b200_launch_count(void);
+
 /* Output extent of a layer; ADDER_ERR_BAD_SHAPE if the geometry is invalid.
  * Replaces the size arithmetic of adder2d_function (adder.py:26-31). */
 ADDER_API int adder_b200_output_size(int h, int w, int k, int stride, int pad, int* ho, int* wo);
