@@ -399,7 +399,21 @@ def run_gpu_arm(args):
                           "fwd_bwd_gops": 9 * T / (ms * 1e-3) / 1e9, "pct_fp32_peak": 100 * 9 * T / (ms * 1e-3) / fp32_peak,
                           "fwd_gbs": (x_b + w_b + o_b) / (t["fwd"] * 1e-3) / 1e9})
         line["layers"] = sweep
-        line["hbm"] = {"peak_gbs": hbm_peak, "note": "adder layers are FP32-issue bound (54-1460 op/B against a machine balance of ~11 op/B)"}
+        # the two 1x1 stride-2 downsample layers (about 6 op/B): bound by memory traffic, reported as GB/s of
+        # algorithmic bytes (each tensor once; only the sampled quarter of x) against the measured HBM peak
+        hbm_layers = []
+        for shp in ((16, 32, 32, 32, 2, 1, 0), (32, 64, 16, 16, 2, 1, 0)):
+            t = time_layer_ops(256, shp)
+            ci, co, h, w, s, k, p = shp
+            x_b, g_b, w_b = 256 * ci * h * w * 4, 256 * co * (h // 2) * (w // 2) * 4, co * ci * 4
+            by = {"fwd": x_b // 4 + w_b + g_b, "grad_x": g_b + x_b // 4 + w_b + x_b, "grad_w": g_b + x_b // 4 + 2 * w_b}
+            hbm_layers.append({"shape": {"ci": ci, "co": co, "h": h, "w": w, "stride": s, "k": k},
+                               **{f"{op}_ms": t[op] for op in ("fwd", "grad_x", "grad_w", "bwd")},
+                               **{f"{op}_gbs": by[op] / (t[op] * 1e-3) / 1e9 for op in by},
+                               **{f"{op}_frac_hbm": by[op] / (t[op] * 1e-3) / 1e9 / hbm_peak for op in by}})
+        line["hbm_layers"] = hbm_layers
+        line["hbm"] = {"peak_gbs": hbm_peak, "note": "the 3x3 and the wide 1x1 adder layers are FP32-issue bound (54-1460 op/B against a "
+                       "machine balance of ~11 op/B); the 1x1 stride-2 downsample layers are in hbm_layers"}
 
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
         ips, b, s_per_step = cpu_images_per_s(args.cpu_budget_s, 2, 1)
