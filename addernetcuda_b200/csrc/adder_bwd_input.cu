@@ -115,6 +115,23 @@ __global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
 #pragma unroll
     for (int c = 0; c < RC; ++c) {
         const int ci = ci0 + cig * RC + c;
+        if (S == 1 && RW % 4 == 0 && a.vec_io) {
+            // W and the segment start are multiples of 4 and the tensors 16-byte aligned: whole quads
+            const bool okr = active && n < a.g.N && ci < a.g.Ci && hi < a.g.H;
+            const float* xr = a.x + ((size_t)(n * a.g.Ci + ci) * HW + hi * a.g.W + q0);
+#pragma unroll
+            for (int j = 0; j < RW; j += 4) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (okr && q0 + j < a.g.W) v = __ldg(reinterpret_cast<const float4*>(xr + j));
+                xv[c][j] = FAST ? -0.5f * v.x : v.x;
+                xv[c][j + 1] = FAST ? -0.5f * v.y : v.y;
+                xv[c][j + 2] = FAST ? -0.5f * v.z : v.z;
+                xv[c][j + 3] = FAST ? -0.5f * v.w : v.w;
+            }
+#pragma unroll
+            for (int j = 0; j < RW; ++j) acc[c][j] = 0.f;
+            continue;
+        }
 #pragma unroll
         for (int j = 0; j < RW; ++j) {
             const int wi = (q0 + j) * S + pw;
@@ -129,32 +146,62 @@ __global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
     }
 
     const int nchunks = ceil_div(a.g.Co, a.CKO);
-    const int w_elems = a.CKO * a.TCI * KK;
+    // weight staging roles: the slab has `pairs` (input channel, tap) pairs per output channel; thread
+    // (wgrp, wpr) handles pairs wpr, wpr + WPP, ... of the output channels wgrp, wgrp + wgroups, ...
+    const int pairs = a.TCI * KK;
+    uint32_t wgrp, wpr;
+    a.d_wpp.divmod(tid, wgrp, wpr);
+    const int wgroups = a.wgroups;
 
     auto fill = [&](int chunk, int stage) {
         const int coc0 = chunk * a.CKO;
         fill_patch(Gs + stage * a.gs_stage, a.gout, a.pd, n0, coc0, go_r0, go_c0, a.g.N, a.g.Co, a.g.Ho, a.g.Wo,
                    tid, nthreads);
+        // weights: a thread owns (input channel, tap) pairs and walks the chunk's output channels, so the
+        // index arithmetic is done once per pair (consecutive pairs are consecutive in global memory)
         float* wt = Wt + stage * a.ws_stage;
-        for (int e = tid; e < w_elems; e += nthreads) {
-            uint32_t col, q, cil, tap;
-            a.d_tcikk.divmod(e, col, q);
-            a.d_kk.divmod(q, cil, tap);
-            const int co = coc0 + col, ci = ci0 + cil;
-            const bool ok = (co < a.g.Co) & (ci < a.g.Ci);
-            const float* src = ok ? a.w + ((size_t)(co * a.g.Ci + ci) * KK + tap) : a.w;
-            cp_async4(wt + (col * KK + tap) * a.TCIP + cil, src, ok);
+        const int ncol = min(a.CKO, a.g.Co - coc0);
+        if constexpr (KS == 1) {
+            // 1x1: the slab is [CKO][TCI]; a flat element loop measured faster here
+            for (int e = tid; e < a.CKO * a.TCI; e += nthreads) {
+                uint32_t col, cil;
+                a.d_tci.divmod(e, col, cil);
+                const int co = coc0 + col, ci = ci0 + cil;
+                const bool ok = (co < a.g.Co) & (ci < a.g.Ci);
+                cp_async4(wt + col * a.TCIP + cil, ok ? a.w + ((size_t)co * a.g.Ci + ci) : a.w, ok);
+            }
+        } else if ((int)wgrp < wgroups) {
+            for (int pr = wpr; pr < pairs; pr += a.WPP) {
+                uint32_t cil, tap;
+                a.d_kk.divmod(pr, cil, tap);
+                const int ci = ci0 + cil;
+                const bool okc = ci < a.g.Ci;
+                const float* src = a.w + ((size_t)coc0 * a.g.Ci + (okc ? ci : 0)) * KK + tap;
+                float* dst = wt + tap * a.TCIP + cil;
+                for (int col = wgrp; col < a.CKO; col += wgroups) {
+                    const bool ok = okc & (col < ncol);
+                    cp_async4(dst + col * KK * a.TCIP, ok ? src + (size_t)col * a.g.Ci * KK : a.w, ok);
+                }
+            }
         }
     };
     // FAST: turn the weights this thread copied into w/2 + 1/2 once they have landed.
     auto scale_weights = [&](int stage) {
         float* wt = Wt + stage * a.ws_stage;
-        for (int e = tid; e < w_elems; e += nthreads) {
-            uint32_t col, q, cil, tap;
-            a.d_tcikk.divmod(e, col, q);
-            a.d_kk.divmod(q, cil, tap);
-            float* p = wt + (col * KK + tap) * a.TCIP + cil;
-            *p = fmaf(*p, 0.5f, 0.5f);
+        if constexpr (KS == 1) {
+            for (int e = tid; e < a.CKO * a.TCI; e += nthreads) {
+                uint32_t col, cil;
+                a.d_tci.divmod(e, col, cil);
+                float* p = wt + col * a.TCIP + cil;
+                *p = fmaf(*p, 0.5f, 0.5f);
+            }
+        } else if ((int)wgrp < wgroups) {
+            for (int pr = wpr; pr < pairs; pr += a.WPP) {
+                uint32_t cil, tap;
+                a.d_kk.divmod(pr, cil, tap);
+                float* p = wt + tap * a.TCIP + cil;
+                for (int col = wgrp; col < a.CKO; col += wgroups) p[col * KK * a.TCIP] = fmaf(p[col * KK * a.TCIP], 0.5f, 0.5f);
+            }
         }
     };
 
@@ -269,23 +316,27 @@ __global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
                         acc2[cc / 2][j] = 0ull;
                     }
             }
+            if (KS == 1 || nchunks > 1) {      // a single chunk's sums stay in registers (3x3 kernels)
 #pragma unroll
-            for (int cc = 0; cc < RC; ++cc)
+                for (int cc = 0; cc < RC; ++cc)
 #pragma unroll
-                for (int j = 0; j < RW; ++j) {
-                    float* t = Tot + (cc * RW + j) * nthreads;
-                    *t = (c == 0 ? 0.f : *t) + acc[cc][j];
-                    acc[cc][j] = 0.f;
-                }
+                    for (int j = 0; j < RW; ++j) {
+                        float* t = Tot + (cc * RW + j) * nthreads;
+                        *t = (c == 0 ? 0.f : *t) + acc[cc][j];
+                        acc[cc][j] = 0.f;
+                    }
+            }
         }
         __syncthreads();
     }
 
     if (!active || n >= a.g.N || hi >= a.g.H) return;
+    if (KS == 1 || nchunks > 1) {
 #pragma unroll
-    for (int cc = 0; cc < RC; ++cc)
+        for (int cc = 0; cc < RC; ++cc)
 #pragma unroll
-        for (int j = 0; j < RW; ++j) acc[cc][j] = Tot[(cc * RW + j) * nthreads];
+            for (int j = 0; j < RW; ++j) acc[cc][j] = Tot[(cc * RW + j) * nthreads];
+    }
     float box[RW];
     if (FAST) {
         // sum of g over the taps of each pixel = box sum of the channel-summed patch
@@ -312,6 +363,24 @@ __global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
         const int ci = ci0 + cig * RC + c;
         if (ci >= a.g.Ci) break;
         float* o = a.gx + ((size_t)(n * a.g.Ci + ci) * HW + hi * a.g.W);
+        if (S == 1 && RW % 4 == 0 && a.vec_io) {
+#pragma unroll
+            for (int j = 0; j < RW; j += 4) {
+                if (q0 + j >= a.g.W) break;
+                float4 v;
+                v.x = FAST ? 2.f * acc[c][j] - box[j] : acc[c][j];
+                v.y = FAST ? 2.f * acc[c][j + 1] - box[j + 1] : acc[c][j + 1];
+                v.z = FAST ? 2.f * acc[c][j + 2] - box[j + 2] : acc[c][j + 2];
+                v.w = FAST ? 2.f * acc[c][j + 3] - box[j + 3] : acc[c][j + 3];
+                float4* o4 = reinterpret_cast<float4*>(o + q0 + j);
+                if (a.accumulate) {
+                    const float4 old = *o4;
+                    v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                }
+                *o4 = v;
+            }
+            continue;
+        }
 #pragma unroll
         for (int j = 0; j < RW; ++j) {
             const int wi = (q0 + j) * S + pw;
@@ -451,7 +520,10 @@ static int plan_gx_t(const Geom& g, const TileHint& hint, GxPlan& p) {
     a.class_major = (S > 1 && a.TH % S == 0) ? 1 : 0;
     a.d_ths = FastDiv(a.class_major ? a.TH / S : 1);
     a.d_ti = FastDiv(a.TI);
-    a.d_tcikk = FastDiv(a.TCI * KS * KS);
+    a.WPP = a.TCI * KS * KS < threads ? a.TCI * KS * KS : threads;
+    a.wgroups = threads / a.WPP;
+    a.d_wpp = FastDiv(a.WPP);
+    a.d_tci = FastDiv(a.TCI);
     a.d_kk = FastDiv(KS * KS);
     const long long gxd = (long long)ceil_div(g.N, a.TI) * a.tiles_h * a.tiles_w;
     const int gyd = ceil_div(g.Ci, a.TCI);
@@ -467,6 +539,8 @@ static int launch_gx_t(const Geom& g, const float* gout, const float* x, const f
     const int st = plan_gx_t<KS, S, RW, RC, FAST>(g, hint, p);
     if (st != ADDER_OK) return st;
     p.a.gout = gout; p.a.x = x; p.a.w = w; p.a.gx = gx; p.a.accumulate = accumulate;
+    p.a.vec_io = (S == 1 && RW % 4 == 0 && g.W % 4 == 0 &&
+                  ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(gx)) & 15) == 0) ? 1 : 0;
     auto kern = adder_gx_kernel<KS, S, RW, RC, FAST>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem) != cudaSuccess)
         return ADDER_ERR_CUDA;

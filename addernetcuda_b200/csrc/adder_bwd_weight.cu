@@ -74,8 +74,12 @@ __global__ void __launch_bounds__(256, GW_MIN_BLOCKS) adder_gw_kernel(const GwAr
         const int n0 = tn * a.TI, ho0 = th * a.TH, wo0 = tw * (a.SPR * RW);
         fill_patch(Xs + stage * a.xs_stage, a.x, a.pdx, n0, ci0, ho0 * S - a.g.pad, wo0 * S - a.g.pad, a.g.N,
                    a.g.Ci, a.g.H, a.g.W, tid, nthreads);
-        fill_patch(Gs + stage * a.gs_stage, a.gout, a.pdg, n0, co0, ho0, wo0, a.g.N, a.g.Co, a.g.Ho, a.g.Wo, tid,
-                   nthreads);
+        if (a.g_quads)
+            fill_patch_quads(Gs + stage * a.gs_stage, a.gout, a.pdg, a.d_gquads, n0, co0, ho0, wo0, a.g.N, a.g.Co, a.g.Ho,
+                             a.g.Wo, tid, nthreads);
+        else
+            fill_patch(Gs + stage * a.gs_stage, a.gout, a.pdg, n0, co0, ho0, wo0, a.g.N, a.g.Co, a.g.Ho, a.g.Wo, tid,
+                       nthreads);
     };
 
     if (t_begin < t_end) {
@@ -424,6 +428,11 @@ static GwPlan plan_gw_t(const Geom& g, const TileHint& hint) {
     a.tiles_rem = a.tiles_total % splits;
     px.d_cols = FastDiv(px.COLS); px.d_rows = FastDiv(px.ROWS);
     pg.d_cols = FastDiv(pg.COLS); pg.d_rows = FastDiv(pg.ROWS);
+    // the g tile has no halo: 16-byte copies when its rows start on 16-byte boundaries in both memories
+    // (the pointer's alignment is checked at launch)
+    a.g_quads = (pg.COLS % 4 == 0 && pg.PITCH % 4 == 0 && g.Wo % 4 == 0 && (a.SPR * RW) % 4 == 0 &&
+                 (a.TI * pg.ROWS_PITCH) % 4 == 0) ? 1 : 0;
+    a.d_gquads = FastDiv(pg.COLS >= 4 ? pg.COLS / 4 : 1);
     a.d_tiles_h = FastDiv(a.tiles_h);
     a.d_tiles_w = FastDiv(a.tiles_w);
     a.d_spr = FastDiv(a.SPR);
@@ -506,6 +515,7 @@ int launch_gw(const Geom& g, const float* gout, const float* x, const float* w, 
     const size_t CoK = (size_t)g.Co * g.Ci * g.k * g.k;
     float* ws = static_cast<float*>(workspace);
     p.a.gout = gout; p.a.x = x;
+    if ((reinterpret_cast<uintptr_t>(gout) & 15) != 0) p.a.g_quads = 0;
     p.a.part = ws;
     p.a.gsum_part = ws + align_up((size_t)p.a.splits * CoK, 64);
     float* norm_part = p.a.gsum_part + align_up((size_t)p.a.splits * g.Co, 64);

@@ -42,7 +42,9 @@ struct GxArgs {
     PatchDims pd;        // patch of g staged per output-channel chunk
     int TI, TH, SPRC, SPR, SEGS, CGI, TCI, TCIP, CKO, CH_STRIDE;
     int gs_stage, ws_stage, g1_size, tiles_h, tiles_w, accumulate, class_major;
-    FastDiv d_tiles_h, d_tiles_w, d_segs, d_spr, d_sprc, d_th, d_ths, d_ti, d_tcikk, d_kk;
+    FastDiv d_tiles_h, d_tiles_w, d_segs, d_spr, d_sprc, d_th, d_ths, d_ti, d_wpp, d_kk, d_tci;
+    int vec_io;          // x is read and grad_x written as aligned quads
+    int WPP, wgroups;    // weight staging: pairs per pass and output-channel groups (adder_bwd_input.cu)
 };
 
 struct GwArgs {
@@ -59,7 +61,8 @@ struct GwArgs {
     int PL;                       // pixel lanes: threads that share one output tile and split the segments
     int XCH_STRIDE, GCH_STRIDE;
     int xs_stage, gs_stage, tiles_h, tiles_w, tiles_total, splits, tiles_per_split, tiles_rem, n_ci_tiles;
-    FastDiv d_tiles_h, d_tiles_w, d_spr, d_th, d_pl, d_cgo, d_ci_tiles;
+    FastDiv d_tiles_h, d_tiles_w, d_spr, d_th, d_pl, d_cgo, d_ci_tiles, d_gquads;
+    int g_quads;         // the g tile is staged with 16-byte copies
 };
 
 struct GwFinishArgs {

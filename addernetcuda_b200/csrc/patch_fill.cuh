@@ -36,4 +36,32 @@ __device__ __forceinline__ void fill_patch(float* dst, const float* __restrict__
     }
 }
 
+// The same copy in 16-byte pieces, for patches without a halo whose rows start on a 16-byte boundary in
+// both memories: COLS, PITCH, col0 and Ws multiples of 4, src 16-byte aligned, row0/col0 >= 0 not
+// required (a quad is either wholly inside the row or wholly outside it, because Ws % 4 == 0).
+// `d_quads` divides by COLS / 4.
+__device__ __forceinline__ void fill_patch_quads(float* dst, const float* __restrict__ src, const PatchDims& p,
+                                                 const FastDiv& d_quads, int n0, int c0, int row0, int col0, int N,
+                                                 int C, int Hs, int Ws, int tid, int nthreads) {
+    const int qcols = p.COLS >> 2;
+    const int plane_quads = p.TI * p.ROWS * qcols;
+    const int plane = Hs * Ws;
+    const int ch_stride = p.TI * p.ROWS_PITCH;
+    const int nch = C - c0 < p.CH ? C - c0 : p.CH;
+    for (int e = tid; e < plane_quads; e += nthreads) {
+        uint32_t rho, q, i, r;
+        d_quads.divmod(e, rho, q);
+        p.d_rows.divmod(rho, i, r);
+        const int n = n0 + (int)i, row = row0 + (int)r, col = col0 + 4 * (int)q;
+        const bool ok = (n < N) & (row >= 0) & (row < Hs) & (col >= 0) & (col < Ws);
+        const float* s = ok ? src + ((size_t)(n * C + c0) * plane + row * Ws + col) : src;
+        float* d = dst + i * p.ROWS_PITCH + r * p.PITCH + 4 * q;
+#pragma unroll 4
+        for (int c = 0; c < p.CH; ++c) {
+            const bool okc = ok & (c < nch);
+            cp_async16(d + c * ch_stride, okc ? s + (size_t)c * plane : src, okc);
+        }
+    }
+}
+
 }  // namespace adder
