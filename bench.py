@@ -49,7 +49,7 @@ RESNET20_LAYERS = [
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, 16->16 32x32 k3 layer at batch 256 (ncu --set full)
-NCU_DRAM_BYTES = {"adder_fwd_kernel": 16816640, "adder_gx_kernel": 33620992, "adder_gw_kernel": 33589760}
+NCU_DRAM_BYTES = {"adder_fwd_kernel": 16816384, "adder_gx_kernel": 33628160, "adder_gw_kernel": 33596672}
 # 4*(|x|+|w|+|out|), 4*(|g|+|x|+|w|+|gx|), 4*(|g|+|x|+|w|+|gw|) for that layer
 ALGO_BYTES_16x16 = {"adder_fwd_kernel": 33563648, "adder_gx_kernel": 50340864, "adder_gw_kernel": 33572864}
 
