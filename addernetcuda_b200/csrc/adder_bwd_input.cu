@@ -392,6 +392,215 @@ __global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
     }
 }
 
+// Stride-2 3x3 layers, balanced.  The four classes of input pixels (row offset mod 2, column parity)
+// have 1, 2, 2 and 4 valid taps, so warps that each hold one class finish at very different times and
+// wait for each other at every chunk barrier.  Here a thread owns TWO segments of the same row pair and
+// column range: one of class c and one of the complementary class 3 - c (1 + 4 or 2 + 2 taps), so every
+// warp carries 5 or 4 taps per pixel pair.  Everything else (staging, FAST form, two-level sums) is as in
+// adder_gx_kernel; the thread-to-segment map is the class-major one with half as many classes.
+template <int KS, int RW, int RC, bool FAST>
+__global__ void __launch_bounds__(256, 2) adder_gx_s2pair_kernel(const GxArgs a) {
+    constexpr int S = 2, KK = KS * KS, NSEG = 2;
+    extern __shared__ __align__(16) float smem[];
+    float* const Gs = smem;
+    float* const Wt = smem + 2 * a.gs_stage;
+    float* const G1 = Wt + 2 * a.ws_stage;
+    float* const Tot = G1 + a.g1_size + threadIdx.x;   // [NSEG*RC*RW][blockDim.x]
+
+    const int tid = threadIdx.x;
+    const int nthreads = blockDim.x;
+    uint32_t tn, th, tw, tnh;
+    a.d_tiles_w.divmod(blockIdx.x, tnh, tw);
+    a.d_tiles_h.divmod(tnh, tn, th);
+    const int n0 = tn * a.TI;
+    const int hi0 = th * a.TH;
+    const int wq0 = tw * (a.SPRC * RW);
+    const int ci0 = blockIdx.y * a.TCI;
+    const int pad = a.g.pad;
+    const int go_r0 = floor_div(hi0 + pad - (KS - 1), S);
+    const int go_c0 = floor_div(wq0 * S + pad - (KS - 1), S);
+
+    uint32_t cig, seg, t, t2, ws, hr2, cls, img;
+    a.d_segs.divmod(tid, cig, seg);            // d_segs divides by the segments per thread set (SEGS / 2)
+    a.d_sprc.divmod(seg, t, ws);
+    a.d_ths.divmod(t, t2, hr2);
+    a.d_ti.divmod(t2, cls, img);               // cls in {0, 1}: TI*(TH/2)*SPRC consecutive threads share it
+    const bool active = (int)cig < a.CGI;
+    const int n = n0 + img;
+    const int q0 = wq0 + ws * RW;
+    const int HW = a.g.H * a.g.W;
+    int pwv[NSEG], hiv[NSEG], tapcls[NSEG], row0v[NSEG], col0v[NSEG];
+#pragma unroll
+    for (int sg = 0; sg < NSEG; ++sg) {
+        const int c = sg == 0 ? (int)cls : 3 - (int)cls;
+        pwv[sg] = c & 1;
+        hiv[sg] = hi0 + (int)hr2 * 2 + (c >> 1);
+        const int ph = (hiv[sg] + pad) & 1, pwp = (pwv[sg] + pad) & 1;
+        tapcls[sg] = ph * 2 + pwp;
+        row0v[sg] = (hiv[sg] + pad - ph) / 2 - go_r0;
+        col0v[sg] = q0 + (pwv[sg] + pad - pwp) / 2 - go_c0;
+    }
+
+    float xv[NSEG][RC][RW], acc[NSEG][RC][RW];
+#pragma unroll
+    for (int sg = 0; sg < NSEG; ++sg)
+#pragma unroll
+        for (int c = 0; c < RC; ++c) {
+            const int ci = ci0 + cig * RC + c;
+#pragma unroll
+            for (int j = 0; j < RW; ++j) {
+                const int wi = (q0 + j) * S + pwv[sg];
+                const bool ok = active && n < a.g.N && ci < a.g.Ci && hiv[sg] < a.g.H && wi < a.g.W;
+                const float v = ok ? __ldg(a.x + ((size_t)(n * a.g.Ci + ci) * HW + hiv[sg] * a.g.W + wi)) : 0.f;
+                xv[sg][c][j] = FAST ? -0.5f * v : v;
+                acc[sg][c][j] = 0.f;
+            }
+        }
+    if (FAST) {
+        for (int e = tid; e < a.g1_size; e += nthreads) G1[e] = 0.f;
+    }
+
+    const int nchunks = ceil_div(a.g.Co, a.CKO);
+    const int pairs = a.TCI * KK;
+    uint32_t wgrp, wpr;
+    a.d_wpp.divmod(tid, wgrp, wpr);
+    const int wgroups = a.wgroups;
+
+    auto fill = [&](int chunk, int stage) {
+        const int coc0 = chunk * a.CKO;
+        fill_patch(Gs + stage * a.gs_stage, a.gout, a.pd, n0, coc0, go_r0, go_c0, a.g.N, a.g.Co, a.g.Ho, a.g.Wo,
+                   tid, nthreads);
+        float* wt = Wt + stage * a.ws_stage;
+        const int ncol = min(a.CKO, a.g.Co - coc0);
+        if ((int)wgrp < wgroups) {
+            for (int pr = wpr; pr < pairs; pr += a.WPP) {
+                uint32_t cil, tap;
+                a.d_kk.divmod(pr, cil, tap);
+                const int ci = ci0 + cil;
+                const bool okc = ci < a.g.Ci;
+                const float* src = a.w + ((size_t)coc0 * a.g.Ci + (okc ? ci : 0)) * KK + tap;
+                float* dst = wt + tap * a.TCIP + cil;
+                for (int col = wgrp; col < a.CKO; col += wgroups) {
+                    const bool ok = okc & (col < ncol);
+                    cp_async4(dst + col * KK * a.TCIP, ok ? src + (size_t)col * a.g.Ci * KK : a.w, ok);
+                }
+            }
+        }
+    };
+    auto scale_weights = [&](int stage) {      // FAST: w -> w/2 + 1/2, each thread the elements it copied
+        float* wt = Wt + stage * a.ws_stage;
+        if ((int)wgrp < wgroups) {
+            for (int pr = wpr; pr < pairs; pr += a.WPP) {
+                uint32_t cil, tap;
+                a.d_kk.divmod(pr, cil, tap);
+                float* p = wt + tap * a.TCIP + cil;
+                for (int col = wgrp; col < a.CKO; col += wgroups) p[col * KK * a.TCIP] = fmaf(p[col * KK * a.TCIP], 0.5f, 0.5f);
+            }
+        }
+    };
+
+    fill(0, 0);
+    cp_async_commit();
+    for (int c = 0; c < nchunks; ++c) {
+        if (c + 1 < nchunks) {
+            fill(c + 1, (c + 1) & 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        if (FAST) scale_weights(c & 1);
+        __syncthreads();
+        const float* gs = Gs + (c & 1) * a.gs_stage;
+        if (FAST) {
+            for (int e = tid; e < a.g1_size; e += nthreads) {
+                float sum = 0.f;
+                for (int col = 0; col < a.CKO; ++col) sum += gs[col * a.CH_STRIDE + e];
+                G1[e] += sum;
+            }
+        }
+        if (active) {
+            const int ncol = min(a.CKO, a.g.Co - c * a.CKO);
+            const float* gimg = gs + img * a.pd.ROWS_PITCH;
+            const float* wt = Wt + (c & 1) * a.ws_stage + cig * RC;
+#pragma unroll 1
+            for (int col = 0; col < ncol; ++col) {
+                const float* gch = gimg + col * a.CH_STRIDE;
+                const float* wch = wt + col * KK * a.TCIP;
+#pragma unroll
+                for (int sg = 0; sg < NSEG; ++sg) {
+                    switch (tapcls[sg]) {       // uniform across a warp
+                        case 0: gx_taps_stride2<KS, RW, RC, FAST, 0, 0>(acc[sg], xv[sg], gch, wch, row0v[sg], col0v[sg], a.pd.PITCH, a.TCIP); break;
+                        case 1: gx_taps_stride2<KS, RW, RC, FAST, 0, 1>(acc[sg], xv[sg], gch, wch, row0v[sg], col0v[sg], a.pd.PITCH, a.TCIP); break;
+                        case 2: gx_taps_stride2<KS, RW, RC, FAST, 1, 0>(acc[sg], xv[sg], gch, wch, row0v[sg], col0v[sg], a.pd.PITCH, a.TCIP); break;
+                        default: gx_taps_stride2<KS, RW, RC, FAST, 1, 1>(acc[sg], xv[sg], gch, wch, row0v[sg], col0v[sg], a.pd.PITCH, a.TCIP); break;
+                    }
+                }
+            }
+            if (nchunks > 1) {      // two-level summation, as in adder_gx_kernel
+#pragma unroll
+                for (int sg = 0; sg < NSEG; ++sg)
+#pragma unroll
+                    for (int cc = 0; cc < RC; ++cc)
+#pragma unroll
+                        for (int j = 0; j < RW; ++j) {
+                            float* tp = Tot + ((sg * RC + cc) * RW + j) * nthreads;
+                            *tp = (c == 0 ? 0.f : *tp) + acc[sg][cc][j];
+                            acc[sg][cc][j] = 0.f;
+                        }
+            }
+        }
+        __syncthreads();
+    }
+
+    if (!active || n >= a.g.N) return;
+#pragma unroll
+    for (int sg = 0; sg < NSEG; ++sg) {
+        const int hi = hiv[sg], pw = pwv[sg];
+        if (hi >= a.g.H) continue;
+        if (nchunks > 1) {
+#pragma unroll
+            for (int cc = 0; cc < RC; ++cc)
+#pragma unroll
+                for (int j = 0; j < RW; ++j) acc[sg][cc][j] = Tot[((sg * RC + cc) * RW + j) * nthreads];
+        }
+        float box[RW];
+        if (FAST) {
+#pragma unroll
+            for (int j = 0; j < RW; ++j) box[j] = 0.f;
+            const float* g1 = G1 + img * a.pd.ROWS_PITCH;
+#pragma unroll
+            for (int kh = 0; kh < KS; ++kh) {
+                const int tr = hi + pad - kh;
+                if (tr % S != 0) continue;
+                const float* gr = g1 + (tr / S - go_r0) * a.pd.PITCH;
+#pragma unroll
+                for (int kw = 0; kw < KS; ++kw) {
+                    const int tc = pw + pad - kw;
+                    if (tc % S != 0) continue;
+                    const float* gp = gr + (q0 + tc / S - go_c0);
+#pragma unroll
+                    for (int j = 0; j < RW; ++j) box[j] += gp[j];
+                }
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < RC; ++c) {
+            const int ci = ci0 + cig * RC + c;
+            if (ci >= a.g.Ci) break;
+            float* o = a.gx + ((size_t)(n * a.g.Ci + ci) * HW + hi * a.g.W);
+#pragma unroll
+            for (int j = 0; j < RW; ++j) {
+                const int wi = (q0 + j) * S + pw;
+                if (wi < a.g.W) {
+                    const float v = FAST ? 2.f * acc[sg][c][j] - box[j] : acc[sg][c][j];
+                    o[wi] = a.accumulate ? o[wi] + v : v;
+                }
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------
@@ -430,9 +639,11 @@ struct GxPlan {
     int gy;
 };
 
+// nseg = 2: the paired stride-2 kernel (a thread owns two segments of complementary tap classes).
 template <int KS, int S, int RW, int RC, bool FAST>
-static int plan_gx_t(const Geom& g, const TileHint& hint, GxPlan& p) {
+static int plan_gx_n(const Geom& g, const TileHint& hint, GxPlan& p, int nseg) {
     GxArgs& a = p.a;
+    a.nseg = nseg;
     p.ks = KS; p.s = S; p.rw = RW; p.rc = RC; p.fast = FAST;
     a.g = g;
     const int threads_target = hint.threads > 0 ? hint.threads : 256;
@@ -440,7 +651,7 @@ static int plan_gx_t(const Geom& g, const TileHint& hint, GxPlan& p) {
     a.CGI = ceil_div(g.Ci, RC) < cg_max ? ceil_div(g.Ci, RC) : cg_max;
     a.TCI = a.CGI * RC;
     a.TCIP = a.TCI + 4;
-    int segs_target = threads_target / a.CGI;
+    int segs_target = threads_target / a.CGI * nseg;
     if (segs_target < 1) segs_target = 1;
     const int class_px = ceil_div(g.W, S);                 // pixels of one column parity in a row
     const int sprc_full = ceil_div(class_px, RW);
@@ -470,7 +681,8 @@ static int plan_gx_t(const Geom& g, const TileHint& hint, GxPlan& p) {
     }
     if (hint.ti > 0) a.TI = hint.ti;
     a.SEGS = a.TI * a.TH * a.SPR;
-    const int threads = round_up(a.CGI * a.SEGS, 32);
+    if (nseg == 2 && (a.TH % S != 0 || a.SEGS % 2 != 0)) return ADDER_ERR_INTERNAL;   // needs whole row pairs
+    const int threads = round_up(a.CGI * (a.SEGS / nseg), 32);
     p.threads = threads;
     if (threads > 256) return ADDER_ERR_INTERNAL;
     a.tiles_h = ceil_div(g.H, a.TH);
@@ -492,12 +704,12 @@ static int plan_gx_t(const Geom& g, const TileHint& hint, GxPlan& p) {
     a.CH_STRIDE = a.TI * pd.ROWS_PITCH;
     a.g1_size = FAST ? a.CH_STRIDE : 0;
     // shared memory per CTA in proportion to its threads, so that about 16 warps stay resident per SM
-    const int budget_floats = (hint.smem_kb > 0 ? hint.smem_kb : (threads <= 64 ? 26 : threads <= 128 ? 52 : 104)) * 1024 / 4;
+    const int budget_floats = (hint.smem_kb > 0 ? hint.smem_kb : (threads * nseg <= 64 ? 26 : threads * nseg <= 128 ? 52 : 104)) * 1024 / 4;
     int cko = hint.ck > 0 ? hint.ck : (KS == 1 ? 64 : 16);
     if (cko > g.Co) cko = g.Co;
     while (cko > 1) {
         const int need = 2 * (round_up(cko * ti_budget * pd.ROWS_PITCH, 4) + cko * KS * KS * a.TCIP) +
-                         (FAST ? ti_budget * pd.ROWS_PITCH : 0) + RC * RW * threads;
+                         (FAST ? ti_budget * pd.ROWS_PITCH : 0) + RC * RW * threads * nseg;
         if (need <= budget_floats) break;
         --cko;
     }
@@ -506,14 +718,14 @@ static int plan_gx_t(const Geom& g, const TileHint& hint, GxPlan& p) {
     pd.CH = cko;
     a.gs_stage = round_up(cko * a.CH_STRIDE, 4);
     a.ws_stage = cko * KS * KS * a.TCIP;
-    const size_t smem = ((size_t)2 * (a.gs_stage + a.ws_stage) + a.g1_size + (size_t)RC * RW * threads) * sizeof(float);
+    const size_t smem = ((size_t)2 * (a.gs_stage + a.ws_stage) + a.g1_size + (size_t)RC * RW * threads * nseg) * sizeof(float);
     p.smem = smem;
     if (smem > 200 * 1024) return ADDER_ERR_UNSUPPORTED;
     pd.d_cols = FastDiv(pd.COLS);
     pd.d_rows = FastDiv(pd.ROWS);
     a.d_tiles_h = FastDiv(a.tiles_h);
     a.d_tiles_w = FastDiv(a.tiles_w);
-    a.d_segs = FastDiv(a.SEGS);
+    a.d_segs = FastDiv(a.SEGS / nseg);
     a.d_spr = FastDiv(a.SPR);
     a.d_sprc = FastDiv(a.SPRC);
     a.d_th = FastDiv(a.TH);
@@ -533,6 +745,15 @@ static int plan_gx_t(const Geom& g, const TileHint& hint, GxPlan& p) {
 }
 
 template <int KS, int S, int RW, int RC, bool FAST>
+static int plan_gx_t(const Geom& g, const TileHint& hint, GxPlan& p) {
+    // 3x3 stride 2: the paired kernel (4-pixel segments only: wider ones spill with two segments per thread)
+    // unless a tile hint asks for the one-class-per-thread kernel
+    const bool tile_hint = (hint.threads | hint.cg | hint.th | hint.ti | hint.ck | hint.smem_kb) != 0;
+    if (KS == 3 && S == 2 && RW <= 4 && !tile_hint && plan_gx_n<KS, S, RW, RC, FAST>(g, hint, p, 2) == ADDER_OK) return ADDER_OK;
+    return plan_gx_n<KS, S, RW, RC, FAST>(g, hint, p, 1);
+}
+
+template <int KS, int S, int RW, int RC, bool FAST>
 static int launch_gx_t(const Geom& g, const float* gout, const float* x, const float* w, float* gx,
                        int accumulate, const TileHint& hint, cudaStream_t stream) {
     GxPlan p;
@@ -541,6 +762,15 @@ static int launch_gx_t(const Geom& g, const float* gout, const float* x, const f
     p.a.gout = gout; p.a.x = x; p.a.w = w; p.a.gx = gx; p.a.accumulate = accumulate;
     p.a.vec_io = (S == 1 && RW % 4 == 0 && g.W % 4 == 0 &&
                   ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(gx)) & 15) == 0) ? 1 : 0;
+    if constexpr (KS == 3 && S == 2 && RW <= 4) {
+        if (p.a.nseg == 2) {
+            auto kern2 = adder_gx_s2pair_kernel<KS, RW, RC, FAST>;
+            if (cudaFuncSetAttribute(kern2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem) != cudaSuccess)
+                return ADDER_ERR_CUDA;
+            kern2<<<dim3((unsigned)p.gx, (unsigned)p.gy), p.threads, p.smem, stream>>>(p.a);
+            return launched();
+        }
+    }
     auto kern = adder_gx_kernel<KS, S, RW, RC, FAST>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem) != cudaSuccess)
         return ADDER_ERR_CUDA;
@@ -582,9 +812,9 @@ int describe_gx(const Geom& g, int fast, const TileHint& hint, char* buf, size_t
 #undef ADDER_GX_PLAN
     if (st == ADDER_ERR_UNSUPPORTED && !((g.k == 1 || g.k == 3) && (g.stride == 1 || g.stride == 2))) return st;
     snprintf(buf, n,
-             "gx k=%d s=%d RW=%d RC=%d fast=%d CGI=%d TCI=%d TI=%d TH=%d SPRC=%d SEGS=%d CKO=%d rows=%d cols=%d pitch=%d "
+             "gx k=%d s=%d RW=%d RC=%d fast=%d segs/thread=%d CGI=%d TCI=%d TI=%d TH=%d SPRC=%d SEGS=%d CKO=%d rows=%d cols=%d pitch=%d "
              "threads=%d smem=%zu grid=(%lld,%d) status=%d",
-             p.ks, p.s, p.rw, p.rc, p.fast, p.a.CGI, p.a.TCI, p.a.TI, p.a.TH, p.a.SPRC, p.a.SEGS, p.a.CKO, p.a.pd.ROWS,
+             p.ks, p.s, p.rw, p.rc, p.fast, p.a.nseg, p.a.CGI, p.a.TCI, p.a.TI, p.a.TH, p.a.SPRC, p.a.SEGS, p.a.CKO, p.a.pd.ROWS,
              p.a.pd.COLS, p.a.pd.PITCH, p.threads, p.smem, p.gx, p.gy, st);
     return ADDER_OK;
 }

@@ -44,6 +44,7 @@ struct GxArgs {
     int gs_stage, ws_stage, g1_size, tiles_h, tiles_w, accumulate, class_major;
     FastDiv d_tiles_h, d_tiles_w, d_segs, d_spr, d_sprc, d_th, d_ths, d_ti, d_wpp, d_kk, d_tci;
     int vec_io;          // x is read and grad_x written as aligned quads
+    int nseg;            // segments per thread: 2 in the paired stride-2 kernel, else 1
     int WPP, wgroups;    // weight staging: pairs per pass and output-channel groups (adder_bwd_input.cu)
 };
 

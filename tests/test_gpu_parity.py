@@ -271,3 +271,37 @@ def test_pointwise_stride2_kernels(geom, ac):
         lib.adder_b200_set_micro_tile(0, 0, 0)
         lib.adder_b200_set_micro_tile(1, 0, 0)
         lib.adder_b200_set_tile_hint(2, 0, 0, 0, 0, 0, 0)
+
+
+@pytest.mark.parametrize("geom", [(3, 16, 32, 32, 32), (5, 32, 64, 16, 16), (2, 6, 5, 12, 24), (2, 6, 5, 12, 20), (2, 9, 3, 10, 7)],
+                         ids=lambda t: "n%d_c%dto%d_%dx%d" % t)
+def test_stride2_paired_input_gradient(geom, ac):
+    """3x3 stride-2 layers: the kernel in which a thread owns two segments of complementary tap classes
+    (the default where the tile allows whole row pairs) and the one-class-per-thread kernel that a
+    tile hint selects must both match the float64 oracle, exact and saturating-add forms."""
+    from addernetcuda_b200 import _lib
+    lib = _lib.load()
+    n, ci, co, h, w_ = geom
+    gen = torch.Generator().manual_seed(91 + n + ci + co + h)
+    x = torch.randn(n, ci, h, w_, generator=gen)
+    w = torch.randn(co, ci, 3, 3, generator=gen) * 0.5
+    ho, wo = (h + 2 - 3) // 2 + 1, (w_ + 2 - 3) // 2 + 1
+    g = torch.randn(n, co, ho, wo, generator=gen)
+    want_gx, _, _ = O.adder2d_backward_direct(g, x, w, 2, 1)
+    xg, wg, gg = x.to(DEV), w.to(DEV), g.to(DEV)
+    plan = _lib.describe_plan(1, n, ci, h, w_, co, 3, 2, 1, 1)
+    print("   ", plan)
+    if h % 2 == 0 and "RW=4" in plan:      # whole row pairs and 4-pixel segments: the paired kernel
+        assert "segs/thread=2" in plan
+    results = []
+    for fast in (False, True):
+        got = ac.backward_input(gg, xg, wg, 2, 1, fast_clamp=fast)
+        _assert(O.compare("paired grad_x fast=%d" % fast, got, want_gx))
+        results.append(got)
+    try:
+        assert lib.adder_b200_set_tile_hint(1, 256, 0, 0, 0, 0, 0) == 0
+        assert "segs/thread=1" in _lib.describe_plan(1, n, ci, h, w_, co, 3, 2, 1, 1)
+        for fast in (False, True):
+            _assert(O.compare("one-class grad_x fast=%d" % fast, ac.backward_input(gg, xg, wg, 2, 1, fast_clamp=fast), want_gx))
+    finally:
+        lib.adder_b200_set_tile_hint(1, 0, 0, 0, 0, 0, 0)
