@@ -60,6 +60,61 @@ __device__ __forceinline__ void gx_taps_stride2(float (&acc)[RC][RW], const floa
     }
 }
 
+// Weight slab of one output-channel chunk -> shared memory as [col][tap][TCIP] (input channel innermost).
+// 3x3: thread (wgrp, wpr) owns the (input channel, tap) pairs wpr, wpr + WPP, ... and walks the output
+// channels wgrp, wgrp + wgroups, ...: the index arithmetic is done once per pair, and consecutive pairs
+// are consecutive in global memory.  1x1: the slab is [CKO][TCI]; a flat element loop measured faster.
+template <int KS>
+__device__ __forceinline__ void gx_stage_weights(const GxArgs& a, float* wt, int coc0, int ci0, int wgrp, int wpr,
+                                                 int tid, int nthreads) {
+    constexpr int KK = KS * KS;
+    if constexpr (KS == 1) {
+        for (int e = tid; e < a.CKO * a.TCI; e += nthreads) {
+            uint32_t col, cil;
+            a.d_tci.divmod(e, col, cil);
+            const int co = coc0 + col, ci = ci0 + cil;
+            const bool ok = (co < a.g.Co) & (ci < a.g.Ci);
+            cp_async4(wt + col * a.TCIP + cil, ok ? a.w + ((size_t)co * a.g.Ci + ci) : a.w, ok);
+        }
+    } else if (wgrp < a.wgroups) {
+        const int ncol = min(a.CKO, a.g.Co - coc0);
+        for (int pr = wpr; pr < a.TCI * KK; pr += a.WPP) {
+            uint32_t cil, tap;
+            a.d_kk.divmod(pr, cil, tap);
+            const int ci = ci0 + cil;
+            const bool okc = ci < a.g.Ci;
+            const float* src = a.w + ((size_t)coc0 * a.g.Ci + (okc ? ci : 0)) * KK + tap;
+            float* dst = wt + tap * a.TCIP + cil;
+            for (int col = wgrp; col < a.CKO; col += a.wgroups) {
+                const bool ok = okc & (col < ncol);
+                cp_async4(dst + col * KK * a.TCIP, ok ? src + (size_t)col * a.g.Ci * KK : a.w, ok);
+            }
+        }
+    }
+}
+
+// FAST form: every thread turns the weights IT copied into w/2 + 1/2 once its copies have landed
+// (same element-to-thread map as gx_stage_weights, so no barrier is needed in between).
+template <int KS>
+__device__ __forceinline__ void gx_scale_weights(const GxArgs& a, float* wt, int wgrp, int wpr, int tid, int nthreads) {
+    constexpr int KK = KS * KS;
+    if constexpr (KS == 1) {
+        for (int e = tid; e < a.CKO * a.TCI; e += nthreads) {
+            uint32_t col, cil;
+            a.d_tci.divmod(e, col, cil);
+            float* p = wt + col * a.TCIP + cil;
+            *p = fmaf(*p, 0.5f, 0.5f);
+        }
+    } else if (wgrp < a.wgroups) {
+        for (int pr = wpr; pr < a.TCI * KK; pr += a.WPP) {
+            uint32_t cil, tap;
+            a.d_kk.divmod(pr, cil, tap);
+            float* p = wt + tap * a.TCIP + cil;
+            for (int col = wgrp; col < a.CKO; col += a.wgroups) p[col * KK * a.TCIP] = fmaf(p[col * KK * a.TCIP], 0.5f, 0.5f);
+        }
+    }
+}
+
 template <int KS, int S, int RW, int RC, bool FAST>
 __global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
     constexpr int KK = KS * KS;
@@ -146,63 +201,17 @@ __global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
     }
 
     const int nchunks = ceil_div(a.g.Co, a.CKO);
-    // weight staging roles: the slab has `pairs` (input channel, tap) pairs per output channel; thread
-    // (wgrp, wpr) handles pairs wpr, wpr + WPP, ... of the output channels wgrp, wgrp + wgroups, ...
-    const int pairs = a.TCI * KK;
-    uint32_t wgrp, wpr;
+    uint32_t wgrp, wpr;                    // weight staging role of this thread (gx_stage_weights)
     a.d_wpp.divmod(tid, wgrp, wpr);
-    const int wgroups = a.wgroups;
 
     auto fill = [&](int chunk, int stage) {
         const int coc0 = chunk * a.CKO;
         fill_patch(Gs + stage * a.gs_stage, a.gout, a.pd, n0, coc0, go_r0, go_c0, a.g.N, a.g.Co, a.g.Ho, a.g.Wo,
                    tid, nthreads);
-        // weights: a thread owns (input channel, tap) pairs and walks the chunk's output channels, so the
-        // index arithmetic is done once per pair (consecutive pairs are consecutive in global memory)
-        float* wt = Wt + stage * a.ws_stage;
-        const int ncol = min(a.CKO, a.g.Co - coc0);
-        if constexpr (KS == 1) {
-            // 1x1: the slab is [CKO][TCI]; a flat element loop measured faster here
-            for (int e = tid; e < a.CKO * a.TCI; e += nthreads) {
-                uint32_t col, cil;
-                a.d_tci.divmod(e, col, cil);
-                const int co = coc0 + col, ci = ci0 + cil;
-                const bool ok = (co < a.g.Co) & (ci < a.g.Ci);
-                cp_async4(wt + col * a.TCIP + cil, ok ? a.w + ((size_t)co * a.g.Ci + ci) : a.w, ok);
-            }
-        } else if ((int)wgrp < wgroups) {
-            for (int pr = wpr; pr < pairs; pr += a.WPP) {
-                uint32_t cil, tap;
-                a.d_kk.divmod(pr, cil, tap);
-                const int ci = ci0 + cil;
-                const bool okc = ci < a.g.Ci;
-                const float* src = a.w + ((size_t)coc0 * a.g.Ci + (okc ? ci : 0)) * KK + tap;
-                float* dst = wt + tap * a.TCIP + cil;
-                for (int col = wgrp; col < a.CKO; col += wgroups) {
-                    const bool ok = okc & (col < ncol);
-                    cp_async4(dst + col * KK * a.TCIP, ok ? src + (size_t)col * a.g.Ci * KK : a.w, ok);
-                }
-            }
-        }
+        gx_stage_weights<KS>(a, Wt + stage * a.ws_stage, coc0, ci0, (int)wgrp, (int)wpr, tid, nthreads);
     };
-    // FAST: turn the weights this thread copied into w/2 + 1/2 once they have landed.
     auto scale_weights = [&](int stage) {
-        float* wt = Wt + stage * a.ws_stage;
-        if constexpr (KS == 1) {
-            for (int e = tid; e < a.CKO * a.TCI; e += nthreads) {
-                uint32_t col, cil;
-                a.d_tci.divmod(e, col, cil);
-                float* p = wt + col * a.TCIP + cil;
-                *p = fmaf(*p, 0.5f, 0.5f);
-            }
-        } else if ((int)wgrp < wgroups) {
-            for (int pr = wpr; pr < pairs; pr += a.WPP) {
-                uint32_t cil, tap;
-                a.d_kk.divmod(pr, cil, tap);
-                float* p = wt + tap * a.TCIP + cil;
-                for (int col = wgrp; col < a.CKO; col += wgroups) p[col * KK * a.TCIP] = fmaf(p[col * KK * a.TCIP], 0.5f, 0.5f);
-            }
-        }
+        gx_scale_weights<KS>(a, Wt + stage * a.ws_stage, (int)wgrp, (int)wpr, tid, nthreads);
     };
 
     fill(0, 0);
@@ -461,42 +470,17 @@ __global__ void __launch_bounds__(256, 2) adder_gx_s2pair_kernel(const GxArgs a)
     }
 
     const int nchunks = ceil_div(a.g.Co, a.CKO);
-    const int pairs = a.TCI * KK;
-    uint32_t wgrp, wpr;
+    uint32_t wgrp, wpr;                    // weight staging role of this thread (gx_stage_weights)
     a.d_wpp.divmod(tid, wgrp, wpr);
-    const int wgroups = a.wgroups;
 
     auto fill = [&](int chunk, int stage) {
         const int coc0 = chunk * a.CKO;
         fill_patch(Gs + stage * a.gs_stage, a.gout, a.pd, n0, coc0, go_r0, go_c0, a.g.N, a.g.Co, a.g.Ho, a.g.Wo,
                    tid, nthreads);
-        float* wt = Wt + stage * a.ws_stage;
-        const int ncol = min(a.CKO, a.g.Co - coc0);
-        if ((int)wgrp < wgroups) {
-            for (int pr = wpr; pr < pairs; pr += a.WPP) {
-                uint32_t cil, tap;
-                a.d_kk.divmod(pr, cil, tap);
-                const int ci = ci0 + cil;
-                const bool okc = ci < a.g.Ci;
-                const float* src = a.w + ((size_t)coc0 * a.g.Ci + (okc ? ci : 0)) * KK + tap;
-                float* dst = wt + tap * a.TCIP + cil;
-                for (int col = wgrp; col < a.CKO; col += wgroups) {
-                    const bool ok = okc & (col < ncol);
-                    cp_async4(dst + col * KK * a.TCIP, ok ? src + (size_t)col * a.g.Ci * KK : a.w, ok);
-                }
-            }
-        }
+        gx_stage_weights<KS>(a, Wt + stage * a.ws_stage, coc0, ci0, (int)wgrp, (int)wpr, tid, nthreads);
     };
-    auto scale_weights = [&](int stage) {      // FAST: w -> w/2 + 1/2, each thread the elements it copied
-        float* wt = Wt + stage * a.ws_stage;
-        if ((int)wgrp < wgroups) {
-            for (int pr = wpr; pr < pairs; pr += a.WPP) {
-                uint32_t cil, tap;
-                a.d_kk.divmod(pr, cil, tap);
-                float* p = wt + tap * a.TCIP + cil;
-                for (int col = wgrp; col < a.CKO; col += wgroups) p[col * KK * a.TCIP] = fmaf(p[col * KK * a.TCIP], 0.5f, 0.5f);
-            }
-        }
+    auto scale_weights = [&](int stage) {
+        gx_scale_weights<KS>(a, Wt + stage * a.ws_stage, (int)wgrp, (int)wpr, tid, nthreads);
     };
 
     fill(0, 0);
