@@ -687,13 +687,16 @@ static int plan_gx_n(const Geom& g, const TileHint& hint, GxPlan& p, int nseg) {
     pd.ROWS_PITCH = pd.ROWS * pd.PITCH;
     a.CH_STRIDE = a.TI * pd.ROWS_PITCH;
     a.g1_size = FAST ? a.CH_STRIDE : 0;
-    // shared memory per CTA in proportion to its threads, so that about 16 warps stay resident per SM
-    const int budget_floats = (hint.smem_kb > 0 ? hint.smem_kb : (threads * nseg <= 64 ? 26 : threads * nseg <= 128 ? 52 : 104)) * 1024 / 4;
+    // shared memory per CTA in proportion to its threads, so that about 16 warps stay resident per SM.
+    // The thread count used here is the one of a full tile (before TI is clamped to a small batch), so
+    // that the chunk size, and with it the order of summation, does not depend on the batch size.
+    const int threads_full = hint.ti > 0 ? threads : round_up(a.CGI * (ti_budget * a.TH * a.SPR / nseg), 32);
+    const int budget_floats = (hint.smem_kb > 0 ? hint.smem_kb : (threads_full * nseg <= 64 ? 26 : threads_full * nseg <= 128 ? 52 : 104)) * 1024 / 4;
     int cko = hint.ck > 0 ? hint.ck : (KS == 1 ? 64 : 16);
     if (cko > g.Co) cko = g.Co;
     while (cko > 1) {
         const int need = 2 * (round_up(cko * ti_budget * pd.ROWS_PITCH, 4) + cko * KS * KS * a.TCIP) +
-                         (FAST ? ti_budget * pd.ROWS_PITCH : 0) + RC * RW * threads * nseg;
+                         (FAST ? ti_budget * pd.ROWS_PITCH : 0) + RC * RW * threads_full * nseg;
         if (need <= budget_floats) break;
         --cko;
     }
