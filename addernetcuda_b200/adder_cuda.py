@@ -43,12 +43,23 @@ def _stream(dev: torch.device) -> int:
     return torch.cuda.current_stream(dev).cuda_stream
 
 
+_retired: list = []
+
+
 def _workspace(dev: torch.device, nbytes: int) -> torch.Tensor:
     """Per-(device, stream) scratch for the weight-gradient kernels, grown on demand.  Calls on one
-    stream are ordered, so they can share it; allocation goes through torch's caching allocator."""
+    stream are ordered, so they can share it; allocation goes through torch's caching allocator.
+
+    A buffer that has to grow is replaced, never freed: a captured CUDA graph may have baked the old
+    buffer's address into its kernel nodes, and handing that memory back to the allocator would let a
+    later replay write partial sums into someone else's tensor.  Growth is geometric, so the retired
+    buffers of a stream add up to less than the live one."""
     key = (dev.index, _stream(dev))
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
+        if ws is not None:
+            _retired.append(ws)
+            nbytes = max(nbytes, 2 * ws.numel())
         ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
         _workspaces[key] = ws
     return ws

@@ -28,7 +28,8 @@ struct PwArgs {
 };
 
 bool pointwise_applicable(const Geom& g) {
-    return g.k == 1 && g.pad == 0 && g.stride == 2 && g.Ci <= 64 && g.Co <= 64 &&
+    // an empty batch goes to the tiled kernels, whose CTAs write all-zero slices for an empty tile range
+    return g.N >= 1 && g.k == 1 && g.pad == 0 && g.stride == 2 && g.Ci <= 64 && g.Co <= 64 &&
            (long long)g.N * g.Ho * g.Wo < 2147483647LL;
 }
 
@@ -309,7 +310,8 @@ __global__ void __launch_bounds__(PW_THREADS) adder_pw_gw_kernel(const PwGwArgs 
 int pointwise_gw_splits(const Geom& g) {
     const int tiles = ceil_div(g.N * g.Ho * g.Wo, PWG_PT);
     const int target = 4 * sm_count();
-    return tiles < target ? tiles : target;
+    const int splits = tiles < target ? tiles : target;
+    return splits < 1 ? 1 : splits;
 }
 
 int launch_pointwise_gw(const Geom& g, const float* gout, const float* x, float* part, float* gsum_part,

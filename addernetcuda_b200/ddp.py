@@ -12,13 +12,14 @@ Mechanics
   * a post-accumulate hook on each parameter counts arrivals; when a bucket is complete its gradients
     are packed into the flat buffer with one multi-tensor copy, `.grad` is re-pointed at the views,
     and the all-reduce is enqueued on a side stream that waits for the packing only;
-  * `finish()` makes the compute stream wait for the side stream and divides by the world size.
+  * the reduction averages (NCCL's AVG operator), so no scaling pass follows it; `finish()` only makes
+    the compute stream wait for the side stream (with gloo, which can only sum, it also scales).
 Everything is stream-ordered (no host synchronisation), so a whole training step, collectives
 included, can be captured in a CUDA graph.  Works on CPU tensors with the gloo backend (tests).
 """
 from __future__ import annotations
 
-from typing import List
+from typing import List, Optional
 
 import torch
 import torch.distributed as dist
@@ -41,11 +42,16 @@ class _Bucket:
 class BucketedDDP:
     """Gradient bucketing + overlapped all-reduce around an existing module.
 
-        ddp = BucketedDDP(model, bucket_mb=25)
+        ddp = BucketedDDP(model)            # bucket size chosen from the model
         loss = criterion(ddp.module(x), y); loss.backward(); ddp.finish(); optimizer.step()
+
+    `bucket_mb=None` picks the bucket size from the model: a third of the gradient bytes, at most
+    25 MB.  A small network (ResNet-20: 1.09 MB of gradients) then still has three buckets, so the
+    gradients of its last stage are on the wire while the first stage is still in backward; with one
+    big bucket the whole reduction would start after the last gradient and be fully exposed.
     """
 
-    def __init__(self, module: torch.nn.Module, bucket_mb: float = 25.0, process_group=None,
+    def __init__(self, module: torch.nn.Module, bucket_mb: Optional[float] = None, process_group=None,
                  broadcast_from_rank0: bool = True):
         if not dist.is_initialized():
             raise RuntimeError("torch.distributed must be initialised before BucketedDDP")
@@ -61,29 +67,45 @@ class BucketedDDP:
             with torch.no_grad():
                 for t in list(module.parameters()) + list(module.buffers()):
                     dist.broadcast(t, src=0, group=process_group)
-        cap = max(1, int(bucket_mb * 1024 * 1024 / 4))
+        total_bytes = sum(p.numel() * p.element_size() for p in params)
+        if bucket_mb is None:
+            cap_bytes = min(25 * 1024 * 1024, -(-total_bytes // 3))
+        else:
+            cap_bytes = int(bucket_mb * 1024 * 1024)
+        cap_bytes = max(cap_bytes, 1)
+        # reverse registration order (roughly the order gradients become ready); a bucket holds one dtype
         self.buckets: List[_Bucket] = []
         cur: List[torch.nn.Parameter] = []
         size = 0
         for p in reversed(params):
-            if cur and size + p.numel() > cap:
-                self.buckets.append(_Bucket(cur, self.device, p.dtype))
+            nbytes = p.numel() * p.element_size()
+            if cur and (size + nbytes > cap_bytes or p.dtype != cur[0].dtype):
+                self.buckets.append(_Bucket(cur, self.device, cur[0].dtype))
                 cur, size = [], 0
             cur.append(p)
-            size += p.numel()
+            size += nbytes
         if cur:
             self.buckets.append(_Bucket(cur, self.device, cur[0].dtype))
         self._where = {}
+        self._seen = set()       # parameters whose gradient has arrived in the current backward
         for b in self.buckets:
             for p, v in zip(b.params, b.views):
                 self._where[p] = b
                 p._grad_slot = v      # adder layers write their weight gradient straight into the bucket
                 p.register_post_accumulate_grad_hook(self._on_grad)
         self.comm_stream = torch.cuda.Stream(device=self.device) if self.is_cuda else None
+        # NCCL averages inside the reduction; gloo only sums, so its buckets are scaled in finish()
+        self._avg_in_reduce = self.is_cuda and dist.get_backend(process_group) == "nccl"
         self.launch_order: List[int] = []   # bucket indices in the order their all-reduce was enqueued
 
     # ------------------------------------------------------------------ hooks
     def _on_grad(self, p: torch.nn.Parameter) -> None:
+        if p in self._seen:
+            # A weight used twice in one forward accumulates twice: the bucket would be reduced after the
+            # first arrival, and an adder layer's direct write into the bucket slot would overwrite it.
+            raise RuntimeError("BucketedDDP: a parameter received two gradients in one backward pass "
+                               "(shared weights are not supported)")
+        self._seen.add(p)
         b = self._where[p]
         b.pending -= 1
         if b.pending == 0:
@@ -103,7 +125,8 @@ class BucketedDDP:
         if self.is_cuda:
             self.comm_stream.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(self.comm_stream):
-                dist.all_reduce(b.flat, op=dist.ReduceOp.SUM, group=self.group)
+                dist.all_reduce(b.flat, op=dist.ReduceOp.AVG if self._avg_in_reduce else dist.ReduceOp.SUM,
+                                group=self.group)
         else:
             b.work = dist.all_reduce(b.flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
 
@@ -121,10 +144,24 @@ class BucketedDDP:
                     if b.work is not None:
                         b.work.wait()
                         b.work = None
-            with torch.no_grad():
-                torch._foreach_mul_([b.flat for b in self.buckets], 1.0 / self.world)
+            if not self._avg_in_reduce:
+                with torch.no_grad():
+                    torch._foreach_mul_([b.flat for b in self.buckets], 1.0 / self.world)
         for b in self.buckets:
             b.pending = len(b.params)
+        self._seen.clear()
+
+    def sync_buffers(self) -> None:
+        """Average the floating-point buffers (BatchNorm running statistics) over the ranks.  Batch
+        statistics are per rank during training, so the running averages drift apart; call this before
+        evaluating or writing a checkpoint if every rank's copy should be the same."""
+        if self.world == 1:
+            return
+        with torch.no_grad():
+            for t in self.module.buffers():
+                if torch.is_floating_point(t):
+                    dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+                    t.div_(self.world)
 
     def zero_grad(self) -> None:
         """Drop gradients so that the next backward writes fresh ones (set-to-none semantics)."""
@@ -132,3 +169,4 @@ class BucketedDDP:
             for p in b.params:
                 p.grad = None
         self.launch_order.clear()
+        self._seen.clear()

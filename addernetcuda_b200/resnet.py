@@ -176,6 +176,9 @@ def init_seeded(model: nn.Module, seed: int) -> None:
                 fan_in = p.shape[1] * p.shape[2] * p.shape[3]
                 v = rng.standard_normal(tuple(p.shape)).astype(np.float32) * np.float32(math.sqrt(2.0 / fan_in))
                 p.copy_(torch.from_numpy(v))
+            elif p.dim() == 2:     # nn.Linear (the classifier of vgg.py:27-40): Kaiming-normal as well
+                v = rng.standard_normal(tuple(p.shape)).astype(np.float32) * np.float32(math.sqrt(2.0 / p.shape[1]))
+                p.copy_(torch.from_numpy(v))
             elif leaf == "running_var" or (leaf == "weight" and p.dim() == 1):
                 p.fill_(1.0)
             else:

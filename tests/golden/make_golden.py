@@ -33,6 +33,13 @@ from oracle import adder_cuda_cpu, adder_oracle as O, adder_unfold  # noqa: E402
 from tests.cases import LAYER_CASES, COL_CASES, draw_layer, draw_cols, resnet20_batch  # noqa: E402
 
 
+# fixture name, reference module, constructor, batch, input height = width, classes, seed
+NETWORK_FIXTURES = [
+    ("vgg11_bn_b4", "vgg", "vgg11_bn", 4, 32, 10, 1234 + 300),
+    ("resnet50_b4", "resnet50", "resnet50", 4, 224, 1000, 1234 + 500),
+]
+
+
 def import_reference(path: str):
     sys.modules["adder_cuda"] = adder_cuda_cpu
     sys.path.insert(0, path)
@@ -165,17 +172,88 @@ def resnet20_fixture(ref_path: str, batch: int, seed: int):
     lgp, gp = rerun(torch.float32, images * jitter)
     out["noise/logits"] = np.float64(max((lg64 - logits.double()).abs().max().item(),
                                          (lgp - logits).abs().max().item()))
+    # the float64 gradients themselves (rounded to float32 for storage): the anchor for judging an
+    # implementation by ITS distance to exact arithmetic, next to the reference's own distance
+    for k, v in g64.items():
+        out["grad64/" + k] = v.to(torch.float32).numpy()
     for k, v in grads.items():
         out["noise/" + k] = np.float64(max((g64[k] - v.double()).abs().max().item(), (gp[k] - v).abs().max().item()))
     return out
 
 
+def build_on(adder_module, module_name: str, ctor: str):
+    """Import a reference model file with `adder` resolving to `adder_module` and build the network."""
+    saved = sys.modules.get("adder")
+    sys.modules["adder"] = adder_module
+    sys.modules.pop(module_name, None)
+    try:
+        net = getattr(importlib.import_module(module_name), ctor)()
+    finally:
+        sys.modules.pop(module_name, None)
+        if saved is not None:
+            sys.modules["adder"] = saved
+    return net
+
+
+def network_batch(batch, in_hw, classes, seed):
+    """Synthetic image batch ~ N(0,1) [B,3,H,W] with uniform labels (stand-in for CIFAR-10 / ImageNet)."""
+    rng = np.random.default_rng(seed + 7)
+    images = rng.standard_normal((batch, 3, in_hw, in_hw)).astype(np.float32)
+    labels = rng.integers(0, classes, size=(batch,)).astype(np.int64)
+    return images, labels
+
+
+def network_fixture(ref_adder, module_name: str, ctor: str, batch: int, in_hw: int, classes: int, seed: int,
+                    keep: int = 256):
+    """One training step (forward, cross-entropy, backward) of a reference model file, unchanged, on the
+    CPU in float32 through the reference's adder.py; and the same network on the oracle port in float64.
+    Stored: logits, loss, and per parameter a deterministic sample of the gradient (float32 run and
+    float64 run at the same positions) with float64 checksums.  Dropout layers are put in eval mode
+    (identity): a random mask cannot be reproduced across devices."""
+    from addernetcuda_b200 import resnet as R
+    images, labels = network_batch(batch, in_hw, classes, seed)
+    images, labels = t(images), t(labels)
+
+    def run(net, dtype):
+        R.init_seeded(net, seed)
+        net = net.to(dtype).train()
+        for m in net.modules():
+            if isinstance(m, torch.nn.Dropout):
+                m.eval()
+        logits = net(images.to(dtype))
+        loss = torch.nn.functional.cross_entropy(logits, labels)
+        loss.backward()
+        return logits.detach(), loss.detach(), {k: p.grad for k, p in net.named_parameters()}
+
+    lg, loss, grads = run(build_on(ref_adder, module_name, ctor), torch.float32)
+    lg_o, loss_o, grads_o = run(build_on(adder_unfold, module_name, ctor), torch.float32)
+    exact(lg_o, lg, f"{module_name} logits (port)")
+    for k in grads:
+        exact(grads_o[k], grads[k], f"{module_name} grad {k} (port)")
+    lg64, loss64, grads64 = run(build_on(adder_unfold, module_name, ctor), torch.float64)
+    out = {"logits": lg.numpy(), "loss": np.float32(loss.item()), "logits64": lg64.to(torch.float32).numpy(),
+           "loss64": np.float64(loss64.item()), "keys": np.array(list(grads.keys())),
+           "batch": np.int64(batch), "in_hw": np.int64(in_hw), "classes": np.int64(classes), "seed": np.int64(seed)}
+    for k, v in grads.items():
+        idx, val, s1, s2 = subsample(v.numpy(), keep)
+        out[f"grad/{k}.idx"] = idx
+        out[f"grad/{k}.val"] = val
+        out[f"grad/{k}.sumsq"] = s2
+        out[f"grad64/{k}.val"] = grads64[k].numpy().reshape(-1)[idx].astype(np.float32)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("ADDERNET_REFERENCE_DIR", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("ADDERNET_REFERENCE_DIR", ""),
+                    help="checkout of the reference project (or set ADDERNET_REFERENCE_DIR)")
+    ap.add_argument("--skip-layers", action="store_true")
     ap.add_argument("--skip-resnet", action="store_true")
+    ap.add_argument("--skip-networks", action="store_true", help="skip the vgg11_bn and resnet50 fixtures")
     ap.add_argument("--resnet-batches", default="16,256")
     a = ap.parse_args()
+    if not a.reference or not Path(a.reference, "adder.py").exists():
+        raise SystemExit("give the reference checkout with --reference or ADDERNET_REFERENCE_DIR")
     ref_adder = import_reference(a.reference)
     torch.set_num_threads(max(1, torch.get_num_threads()))
     manifest = {"reference": "LingYeAI/AdderNetCUDA", "torch": torch.__version__, "fixtures": []}
@@ -196,14 +274,19 @@ def main():
                 small[f"{prefix}/{k}.sumsq"] = s2
 
     for case in LAYER_CASES:
-        put(case["name"], layer_fixture(ref_adder, case))
         manifest["fixtures"].append(case["name"])
+        if a.skip_layers:
+            continue
+        put(case["name"], layer_fixture(ref_adder, case))
         print("layer", case["name"], "ok")
     for case in COL_CASES:
-        put(case["name"], col_fixture(ref_adder, case))
         manifest["fixtures"].append(case["name"])
+        if a.skip_layers:
+            continue
+        put(case["name"], col_fixture(ref_adder, case))
         print("cols ", case["name"], "ok")
-    np.savez_compressed(HERE / "layers.npz", **small)
+    if not a.skip_layers:
+        np.savez_compressed(HERE / "layers.npz", **small)
 
     if not a.skip_resnet:
         for b in [int(v) for v in a.resnet_batches.split(",")]:
@@ -211,6 +294,15 @@ def main():
             np.savez_compressed(HERE / f"resnet20_b{b}.npz", **fx)
             manifest["fixtures"].append(f"resnet20_b{b}")
             print("resnet20 batch", b, "ok, loss", float(fx["loss"]))
+    # whole networks from the reference's other model files, unchanged: vgg.py (first layer K = 27) and
+    # resnet50.py (the ImageNet bottleneck network), one small-batch training step each
+    for name, module, ctor, batch, hw, classes, seed in NETWORK_FIXTURES:
+        manifest["fixtures"].append(name)
+        if a.skip_networks:
+            continue
+        fx = network_fixture(ref_adder, module, ctor, batch, hw, classes, seed)
+        np.savez_compressed(HERE / f"{name}.npz", **fx)
+        print(name, "ok, loss", float(fx["loss"]))
     (HERE / "MANIFEST.json").write_text(json.dumps(manifest, indent=1) + "\n")
 
 

@@ -51,10 +51,10 @@ def _worker(rank, world, port, q):
             t = p.grad.clone()
             dist.all_reduce(t)
             want[k] = t / world
-        # bucketed, overlapped reduction (two buckets)
+        # bucketed, overlapped reduction; the bucket size comes from the model: three or more buckets
         net = build()
-        ddp = BucketedDDP(net, bucket_mb=0.6)
-        assert len(ddp.buckets) >= 2
+        ddp = BucketedDDP(net)
+        assert len(ddp.buckets) >= 3, len(ddp.buckets)
         ddp.zero_grad()
         torch.nn.functional.cross_entropy(net(images), labels).backward()
         ddp.finish()
@@ -62,6 +62,35 @@ def _worker(rank, world, port, q):
         for k, p in net.named_parameters():
             err = (p.grad - want[k]).abs().max().item()
             assert err <= 1e-6 + 1e-5 * want[k].abs().max().item(), f"{k}: {err}"
+        # the averaged gradients against the CPU oracle: every rank steps the oracle network (the port of
+        # the reference's adder.py) on its own shard in float32 and float64, the per-shard results are
+        # averaged over the ranks, and the data-parallel gradients must match that mean
+        from oracle import adder_unfold as U
+        from tests import netcheck
+        worst = 0.0
+        for dtype in (torch.float32, torch.float64):
+            ora = R.resnet20(conv=U.adder2d)
+            R.init_seeded(ora, 77)
+            ora = ora.to(dtype).train()
+            torch.nn.functional.cross_entropy(ora(images.cpu().to(dtype)), labels.cpu()).backward()
+            mean = {}
+            for k, p in ora.named_parameters():
+                t = p.grad.to(dev, torch.float64)
+                dist.all_reduce(t)
+                mean[k] = (t / world).cpu()
+            if dtype == torch.float32:
+                mean32 = mean
+            else:
+                mean64 = mean
+        anchored = 0
+        for k, p in net.named_parameters():
+            ok, used64, msg = netcheck.grad_ok(k, p.grad, mean32[k], mean64[k])
+            anchored += int(used64)
+            worst = max(worst, (p.grad.double().cpu() - mean32[k]).abs().max().item())
+            assert ok, msg
+        assert anchored <= 3, anchored
+        print(f"rank {rank}: {len(mean32)} averaged gradients match the mean of the per-shard CPU oracle "
+              f"gradients, worst max_abs_err {worst:.3e}, {anchored} judged against float64", flush=True)
         # adder weight gradients were written straight into their bucket slots
         for b in ddp.buckets:
             for p, v in zip(b.params, b.views):

@@ -5,6 +5,7 @@ import pytest
 import torch
 
 from oracle import adder_oracle as O
+from tests import netcheck
 from tests.cases import resnet20_batch
 
 pytestmark = pytest.mark.gpu
@@ -38,34 +39,11 @@ def test_resnet20_step_matches_reference(batch, fast_clamp):
     finally:
         A.FAST_CLAMP = False
     torch.cuda.synchronize()
-    ok, worst, msg = O.compare("logits", logits, torch.from_numpy(z["logits"]))
-    print("   ", msg)
-    assert ok, msg
-    assert abs(float(loss.detach()) - float(z["loss"])) <= 1e-4 + 1e-5 * abs(float(z["loss"]))
-    # Gradients: |got - want| <= 1e-4 + 1e-5*|want|, widened for a tensor only where the reference does
-    # not reproduce ITSELF that closely: `noise/<name>` in the fixture is how far the reference's own
-    # gradient moves between fp32 and fp64 and under a 1e-6 relative perturbation of the images (a few
-    # weight gradients of the last stage are tiny sums of large terms; one ReLU gate flipping upstream
-    # moves them by 1e-3 after the norm rescale).  The layer-level tests pin those layers exactly.
-    worst_name, worst_err, failures, widened = None, 0.0, [], []
-    for k, p in net.named_parameters():
-        want = torch.from_numpy(z["grad/" + k])
-        noise = float(z["noise/" + k])
-        ok, err, msg = O.compare(k, p.grad, want)
-        if err > worst_err:
-            worst_name, worst_err = k, err
-        if not ok:
-            ok2, _, msg2 = O.compare(k, p.grad, want, abs_=1e-4 + 5.0 * noise)
-            if ok2:
-                widened.append(f"{k}: err {err:.2e}, reference self-noise {noise:.2e}")
-            else:
-                failures.append(msg2 + f" (reference self-noise {noise:.2e})")
-    print(f"    worst gradient tensor: {worst_name} max_abs_err={worst_err:.3e} "
-          f"({len(list(net.parameters()))} tensors compared; {len(widened)} judged against reference self-noise)")
-    for wmsg in widened:
-        print("      ", wmsg)
-    assert not failures, "\n".join(failures)
-    assert len(widened) <= 3, widened
+    # logits and loss at the plain tolerance; gradients at the plain tolerance, except that a tensor which
+    # misses it must be at least as close to the float64 evaluation of the step as the reference's own
+    # float32 result is, within a factor of two (tests/netcheck.py)
+    netcheck.check_step(z, logits, float(loss.detach()), [(k, p.grad) for k, p in net.named_parameters()],
+                        sampled=False, max_anchored=3)
 
 
 def test_adder_layers_inside_the_network_match_oracle_on_their_own_inputs():

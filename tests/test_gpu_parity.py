@@ -211,6 +211,26 @@ def test_errors_are_statuses_not_aborts(ac):
     assert ac.forward(torch.zeros(0, 3, 8, 8, device=DEV), torch.randn(4, 3, 3, 3, device=DEV), 1, 1).shape == (0, 4, 8, 8)
 
 
+@pytest.mark.parametrize("geom", [(16, 32, 32, 32, 1, 2, 0), (16, 32, 32, 16, 3, 1, 1), (64, 14, 14, 128, 1, 1, 0)],
+                         ids=lambda t: "c%d_%dx%d_to%d_k%ds%dp%d" % t)
+def test_weight_gradient_of_an_empty_batch_is_zero(geom, ac):
+    """n = 0 through the C ABI: no pixels, so grad_w is all zeros (and stays finite under the rescale)."""
+    from addernetcuda_b200 import _lib
+    lib = _lib.load()
+    ci, h, wd, co, k, s, p = geom
+    g8 = (0, ci, h, wd, co, k, s, p)
+    w = torch.randn(co, ci, k, k, device=DEV)
+    gw = torch.full_like(w, float("nan"))
+    nbytes = lib.adder_b200_backward_weight_workspace_bytes(*g8)
+    assert nbytes > 0
+    ws = torch.empty(nbytes + 256, dtype=torch.uint8, device=DEV)
+    st = lib.adder_b200_backward_weight(None, None, w.data_ptr(), gw.data_ptr(), ctypes.c_float(0.2), None,
+                                        ws.data_ptr(), nbytes, *g8, 0, torch.cuda.current_stream().cuda_stream)
+    assert st == 0, lib.adder_b200_status_string(st)
+    torch.cuda.synchronize()
+    assert torch.equal(gw, torch.zeros_like(gw))
+
+
 @pytest.mark.parametrize("geom", [(3, 16, 32, 32, 32), (2, 32, 64, 16, 16), (2, 5, 7, 9, 11), (1, 33, 20, 6, 5), (2, 64, 64, 8, 8)],
                          ids=lambda t: "n%d_c%dto%d_%dx%d" % t)
 def test_pointwise_stride2_kernels(geom, ac):

@@ -94,3 +94,12 @@ def test_unsupported_geometry_is_reported_not_planned():
     assert lib.adder_b200_describe_plan(0, 4, 8, 16, 16, 8, 5, 1, 2, 0, buf, 256) != 0       # 5x5 kernel
     assert lib.adder_b200_describe_plan(0, 4, 8, 16, 16, 8, 3, 3, 1, 0, buf, 256) != 0       # stride 3
     assert lib.adder_b200_describe_plan(0, 4, 0, 16, 16, 8, 3, 1, 1, 0, buf, 256) != 0       # no channels
+
+
+def test_empty_batch_plans_have_at_least_one_split():
+    """An empty batch still defines the weight gradient (all zeros): the plan must keep one CTA per output
+    tile to write the zero slices, also on the geometry that otherwise takes the pointwise kernels."""
+    for shape in ((0, 16, 32, 32, 32, 1, 2, 0), (0, 16, 32, 32, 16, 3, 1, 1), (0, 1024, 14, 14, 256, 1, 1, 0)):
+        plan = _lib.describe_plan(2, *shape, 0)
+        assert "status=0" in plan and "pointwise=0" in plan, plan
+        assert _field(plan, "splits") >= 1, plan

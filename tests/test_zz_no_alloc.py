@@ -3,9 +3,10 @@
 Some callers cannot give the library a workspace: hosts whose memory manager owns the whole GPU and
 forbids cudaMalloc inside plugins, and bindings that only ever receive input and output pointers.
 For them `adder_b200_backward_weight_static` keeps its scratch in a fixed 8 MiB device array.  This
-test calls it through the C ABI and requires the same gradient as the workspace-taking entry point,
-on two calls in a row with different inputs (the shared array still holds the first call's partial
-sums when the second call starts), and checks that an oversized layer is refused, not overrun.
+test calls it through the C ABI and requires bit-identical gradients to the workspace-taking entry
+point (and agreement with the float64 oracle at the tolerance of the other parity tests), on two calls
+in a row with different inputs (the shared array still holds the first call's partial sums when the
+second call starts), and checks that an oversized layer is refused, not overrun.
 
 The file sorts last on purpose: a run that stops at the first failure has then already executed
 every other test.  It also passes when run alone in a fresh process, where its first call is the
@@ -55,10 +56,14 @@ def test_static_scratch_entry_point_matches_workspace_entry_point():
                                                        ctypes.c_float(0.2), got_norm.data_ptr(), *geom, stream)
             assert st == 0, lib.adder_b200_status_string(st)
             torch.cuda.synchronize()
-            err = (got - want).abs().max().item()
-            bound = (1e-4 + 1e-5 * want.abs()).min().item()
-            assert torch.isfinite(got).all() and err <= bound, f"geom {geom}: max_abs_err {err:.3e}"
-            assert abs(float(got_norm) - float(want_norm)) <= 1e-5 * float(want_norm)
+            # same kernels, same plan, same summation order: the two entry points agree bit for bit
+            assert torch.equal(got, want), f"geom {geom}: max_abs_err {(got - want).abs().max().item():.3e}"
+            assert float(got_norm) == float(want_norm)
+        # and the result is the reference's: rescaled weight gradient from the float64 oracle
+        from oracle import adder_oracle as O
+        _, want_oracle, _ = O.adder2d_backward_direct(g.cpu(), x.cpu(), wt.cpu(), s, p)
+        ok, err, msg = O.compare(f"static-scratch grad_w {geom}", got, want_oracle)
+        assert ok, msg
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit():
