@@ -11,6 +11,7 @@ from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
 LIB_PATH = _PKG / "libadder_b200.so"
+TUNING_LIB_PATH = _PKG / "libadder_b200_tuning.so"
 
 ADDER_OK = 0
 FLAG_FAST_CLAMP = 1
@@ -46,29 +47,64 @@ SIGNATURES = {
                                              c_int, c_int, c_int, c_void_p]),
     "adder_b200_batchnorm_backward": (c_int, [c_void_p] * 10 + [c_int, c_void_p, c_size_t, c_int, c_int, c_int,
                                               c_void_p]),
-    "adder_b200_set_tile_hint": (c_int, [c_int] * 7),
-    "adder_b200_set_micro_tile": (c_int, [c_int, c_int, c_int]),
     "adder_b200_describe_plan": (c_int, [c_int, *_GEOM, c_int, c_char_p, c_size_t]),
 }
+# exported by libadder_b200_tuning.so only (the header's ADDER_B200_TUNING section)
+TUNING_SIGNATURES = {
+    "adder_b200_set_tile_hint": (c_int, [c_int] * 7),
+    "adder_b200_set_micro_tile": (c_int, [c_int, c_int, c_int]),
+    "adder_b200_set_variant": (c_int, [c_int, c_int]),
+}
 
-_lib = None
+_product = None
+_tuning = None
+_active = None
 
 
-def load() -> ctypes.CDLL:
-    """Load (building first if necessary) the shared library and attach the prototypes."""
-    global _lib
-    if _lib is not None:
-        return _lib
-    if not LIB_PATH.exists():
+def _open(path: Path, signatures) -> ctypes.CDLL:
+    if not path.exists():
         from . import build as _build
         _build.build()
-    lib = ctypes.CDLL(str(LIB_PATH))
-    for name, (res, args) in SIGNATURES.items():
+    lib = ctypes.CDLL(str(path))
+    for name, (res, args) in signatures.items():
         fn = getattr(lib, name)   # AttributeError here means header and library disagree
         fn.restype = res
         fn.argtypes = args
-    _lib = lib
     return lib
+
+
+def load() -> ctypes.CDLL:
+    """The library every op of this package calls: the product library, unless a `tuning()` block is
+    active.  Loaded (and built first if necessary) on first use."""
+    global _product, _active
+    if _active is not None:
+        return _active
+    if _product is None:
+        _product = _open(LIB_PATH, SIGNATURES)
+    _active = _product
+    return _active
+
+
+class tuning:
+    """`with tuning() as lib:` routes every op of this package through libadder_b200_tuning.so, whose
+    extra entry points (`lib.adder_b200_set_tile_hint`, `_set_micro_tile`, `_set_variant`) override the
+    tile planners.  On exit all overrides are cleared and the product library is active again."""
+
+    def __enter__(self) -> ctypes.CDLL:
+        global _tuning, _active
+        if _tuning is None:
+            _tuning = _open(TUNING_LIB_PATH, {**SIGNATURES, **TUNING_SIGNATURES})
+        self._previous = _active
+        _active = _tuning
+        return _tuning
+
+    def __exit__(self, *exc) -> None:
+        global _active
+        for op in range(3):
+            _tuning.adder_b200_set_tile_hint(op, 0, 0, 0, 0, 0, 0)
+            _tuning.adder_b200_set_micro_tile(op, 0, 0)
+            _tuning.adder_b200_set_variant(op, 0)
+        _active = self._previous
 
 
 def check(status: int, what: str) -> None:

@@ -4,6 +4,9 @@
 
 The library is placed next to this file so that it travels with the source tree.  It links the
 CUDA runtime statically and exports only the extern "C" entry points of include/adder_b200.h.
+A second library, libadder_b200_tuning.so, is linked from the same objects with the C-ABI layer compiled
+with -DADDER_B200_TUNING: it adds the tile-override setters that parameter sweeps and some tests use and
+that the product library deliberately lacks.
 """
 from __future__ import annotations
 
@@ -18,7 +21,8 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 INCLUDE = PKG.parent / "include"
 LIB = PKG / "libadder_b200.so"
-SOURCES = ["api.cu", "adder_fwd.cu", "adder_bwd_input.cu", "adder_bwd_weight.cu", "adder_bwd_weight_1x1.cu", "adder_pointwise.cu", "static_scratch.cu", "batchnorm.cu"]
+TUNING_LIB = PKG / "libadder_b200_tuning.so"   # same objects, api.cu compiled with -DADDER_B200_TUNING
+SOURCES = ["api.cu", "adder_fwd.cu", "adder_fwd_pipe.cu", "adder_bwd_input.cu", "adder_bwd_input_pipe.cu", "adder_bwd_weight.cu", "adder_bwd_weight_pipe.cu", "adder_bwd_weight_1x1.cu", "adder_pointwise.cu", "static_scratch.cu", "batchnorm.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
@@ -30,9 +34,9 @@ def find_nvcc() -> str:
 
 
 def _stale() -> bool:
-    if not LIB.exists():
+    if not LIB.exists() or not TUNING_LIB.exists():
         return True
-    t = LIB.stat().st_mtime
+    t = min(LIB.stat().st_mtime, TUNING_LIB.stat().st_mtime)
     deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list(INCLUDE.glob("*.h"))
     return any(d.stat().st_mtime > t for d in deps)
 
@@ -55,6 +59,10 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         objs.append(str(obj))
         procs.append((src, subprocess.Popen(common + ["-c", str(CSRC / src), "-o", str(obj)],
                                             stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    # the tuning variant of the C-ABI layer: the only translation unit that differs between the two libraries
+    api_tuning = objdir / "api_tuning.o"
+    procs.append(("api.cu (tuning)", subprocess.Popen(common + ["-DADDER_B200_TUNING", "-c", str(CSRC / "api.cu"), "-o", str(api_tuning)],
+                                                      stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False
     for src, p in procs:
         out, _ = p.communicate()
@@ -67,6 +75,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         raise RuntimeError("nvcc compilation failed")
     link = [nvcc, "-shared", *ARCH_FLAGS, "-o", str(LIB), *objs, "-cudart", "static"]
     subprocess.run(link, check=True)
+    tuning_objs = [str(api_tuning) if o.endswith("/api.o") else o for o in objs]
+    subprocess.run([nvcc, "-shared", *ARCH_FLAGS, "-o", str(TUNING_LIB), *tuning_objs, "-cudart", "static"], check=True)
     return LIB
 
 

@@ -752,15 +752,13 @@ static int launch_gx_t(const Geom& g, const float* gout, const float* x, const f
     if constexpr (KS == 3 && S == 2 && RW <= 4) {
         if (p.a.nseg == 2) {
             auto kern2 = adder_gx_s2pair_kernel<KS, RW, RC, FAST>;
-            if (cudaFuncSetAttribute(kern2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem) != cudaSuccess)
-                return ADDER_ERR_CUDA;
+            if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern2), p.smem) != ADDER_OK) return ADDER_ERR_CUDA;
             kern2<<<dim3((unsigned)p.gx, (unsigned)p.gy), p.threads, p.smem, stream>>>(p.a);
             return launched();
         }
     }
     auto kern = adder_gx_kernel<KS, S, RW, RC, FAST>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem) != cudaSuccess)
-        return ADDER_ERR_CUDA;
+    if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), p.smem) != ADDER_OK) return ADDER_ERR_CUDA;
     kern<<<dim3((unsigned)p.gx, (unsigned)p.gy), p.threads, p.smem, stream>>>(p.a);
     return launched();
 }
@@ -791,6 +789,7 @@ int describe_gx(const Geom& g, int fast, const TileHint& hint, char* buf, size_t
                  "grid=(%d,%d) status=0", g.stride, fast, ceil_div(g.N * g.Ho * g.Wo, 256), ceil_div(g.Ci, 16));
         return ADDER_OK;
     }
+    if (gx_pipe_applicable(g, hint)) return describe_gx_pipe(g, fast, hint, buf, n);
     const int rw = choose_gx_rw(g, hint);
     GxPlan p;
     int st = ADDER_ERR_UNSUPPORTED;
@@ -809,6 +808,7 @@ int describe_gx(const Geom& g, int fast, const TileHint& hint, char* buf, size_t
 int launch_gx(const Geom& g, const float* gout, const float* x, const float* w, float* gx, int fast,
               int accumulate, const TileHint& hint, cudaStream_t stream) {
     if (hint.is_default() && pointwise_applicable(g)) return launch_pointwise_gx(g, gout, x, w, gx, fast, accumulate, stream);
+    if (gx_pipe_applicable(g, hint)) return launch_gx_pipe(g, gout, x, w, gx, fast, accumulate, hint, stream);
     const int rw = choose_gx_rw(g, hint);
 #define ADDER_GX_LAUNCH(KS_, S_, RW_, RC_, FAST_) \
     return launch_gx_t<KS_, S_, RW_, RC_, FAST_>(g, gout, x, w, gx, accumulate, hint, stream);

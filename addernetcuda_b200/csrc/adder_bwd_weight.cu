@@ -329,6 +329,7 @@ struct GwPlan {
     int status;
     bool use_1x1 = false;   // 1x1 stride-1 layers with enough channels take the GEMM-style kernel
     bool use_pointwise = false;   // 1x1 stride-2 layers with few channels: adder_pointwise.cu
+    bool use_pipe = false;        // 3x3 layers with channels in sixteens: adder_bwd_weight_pipe.cu
 };
 
 template <int KS, int S, int RW, int RM, int RC>
@@ -448,6 +449,13 @@ static GwPlan plan_gw_generic(const Geom& g, const TileHint& hint);
 
 static GwPlan plan_gw(const Geom& g, const TileHint& hint) {
     GwPlan p = plan_gw_generic(g, hint);
+    if (p.status == ADDER_OK && gw_pipe_applicable(g, hint)) {
+        const int sp = gw_pipe_splits(g, hint);
+        if (sp > 0) {
+            p.use_pipe = true;
+            p.a.splits = sp;
+        }
+    }
     if (p.status == ADDER_OK && gw1x1_applicable(g) && hint.rm != 9) {
         p.use_1x1 = true;
         p.a.splits = gw1x1_splits(g);
@@ -474,6 +482,7 @@ static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 int describe_gw(const Geom& g, const TileHint& hint, char* buf, size_t n) {
     const GwPlan p = plan_gw(g, hint);
+    if (p.status == ADDER_OK && p.use_pipe) return describe_gw_pipe(g, hint, buf, n);
     if (p.status == ADDER_ERR_UNSUPPORTED && !((g.k == 1 || g.k == 3) && (g.stride == 1 || g.stride == 2))) return p.status;
     const GwArgs& a = p.a;
     snprintf(buf, n,
@@ -497,8 +506,7 @@ size_t gw_workspace_bytes(const Geom& g, const TileHint& hint) {
 template <int KS, int S, int RW, int RM, int RC>
 static int launch_main_t(const GwPlan& p, cudaStream_t stream) {
     auto kern = adder_gw_kernel<KS, S, RW, RM, RC>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem) != cudaSuccess)
-        return ADDER_ERR_CUDA;
+    if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), p.smem) != ADDER_OK) return ADDER_ERR_CUDA;
     const int out_tiles = ceil_div(p.a.g.Co, p.a.TM) * p.a.n_ci_tiles;
     kern<<<dim3((unsigned)p.a.splits, (unsigned)out_tiles), p.threads, p.smem, stream>>>(p.a);
     return launched();
@@ -524,7 +532,8 @@ int launch_gw(const Geom& g, const float* gout, const float* x, const float* w, 
 
     const bool rw7 = (g.Wo % 8 != 0) && (g.Wo % 7 == 0);
     int st = ADDER_ERR_UNSUPPORTED;
-    if (p.use_pointwise) st = launch_pointwise_gw(g, gout, x, p.a.part, p.a.gsum_part, ticket, p.a.splits, stream);
+    if (p.use_pipe) st = launch_gw_pipe(g, gout, x, p.a.part, p.a.gsum_part, ticket, p.a.splits, hint, stream);
+    else if (p.use_pointwise) st = launch_pointwise_gw(g, gout, x, p.a.part, p.a.gsum_part, ticket, p.a.splits, stream);
     else if (p.use_1x1) st = launch_gw1x1(g, gout, x, p.a.part, p.a.gsum_part, ticket, p.a.splits, stream);
     else if (g.k == 3 && g.stride == 1) st = rw7 ? launch_main_t<3, 1, 7, 4, 2>(p, stream) : launch_main_t<3, 1, 8, 4, 2>(p, stream);
     else if (g.k == 3 && g.stride == 2) st = rw7 ? launch_main_t<3, 2, 7, 4, 2>(p, stream) : launch_main_t<3, 2, 8, 4, 2>(p, stream);

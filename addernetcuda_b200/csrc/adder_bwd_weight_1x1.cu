@@ -169,11 +169,11 @@ int launch_gw1x1(const Geom& g, const float* gout, const float* x, float* part, 
     const bool vec = (a.HW % 4 == 0) && (((reinterpret_cast<uintptr_t>(gout) | reinterpret_cast<uintptr_t>(x)) & 15) == 0);
     const dim3 grid(splits, out_tiles);
     if (vec) {
-        if (cudaFuncSetAttribute(adder_gw1x1_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (ensure_dynamic_smem(reinterpret_cast<const void*>(adder_gw1x1_kernel<true>), smem) != ADDER_OK)
             return ADDER_ERR_CUDA;
         adder_gw1x1_kernel<true><<<grid, G1_THREADS, smem, stream>>>(a);
     } else {
-        if (cudaFuncSetAttribute(adder_gw1x1_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (ensure_dynamic_smem(reinterpret_cast<const void*>(adder_gw1x1_kernel<false>), smem) != ADDER_OK)
             return ADDER_ERR_CUDA;
         adder_gw1x1_kernel<false><<<grid, G1_THREADS, smem, stream>>>(a);
     }

@@ -336,7 +336,7 @@ int launch_pointwise_gw(const Geom& g, const float* gout, const float* x, float*
     const size_t stage = (size_t)(a.nco4 + a.nci4) * 4 * PWG_PITCH;
     const size_t red = (size_t)a.PS * a.OT * PWG_RED;
     const size_t smem = (stage > red ? stage : red) * sizeof(float);
-    if (cudaFuncSetAttribute(adder_pw_gw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    if (ensure_dynamic_smem(reinterpret_cast<const void*>(adder_pw_gw_kernel), smem) != ADDER_OK)
         return ADDER_ERR_CUDA;
     adder_pw_gw_kernel<<<splits, PW_THREADS, smem, stream>>>(a);
     return launched();

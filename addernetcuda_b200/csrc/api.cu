@@ -1,13 +1,21 @@
 // extern "C" layer of libadder_b200.so: argument validation, geometry, dispatch to the kernels.
 #include <atomic>
+#include <map>
+#include <mutex>
+#include <utility>
 #include "kernels.h"
 
 using namespace adder;
 
 namespace {
 
+#ifdef ADDER_B200_TUNING
+// Tuning build only (libadder_b200_tuning.so): process-wide overrides of the tile heuristics, set through
+// adder_b200_set_tile_hint / _set_micro_tile / _set_variant.  The product library has none of this: its
+// kernels are always chosen by the planners, and it keeps no mutable state besides the launch counter
+// and the documented static scratch array.
 struct HintSlot {
-    std::atomic<int> threads{0}, cg{0}, th{0}, ti{0}, ck{0}, smem_kb{0}, rw{0}, rm{0};
+    std::atomic<int> threads{0}, cg{0}, th{0}, ti{0}, ck{0}, smem_kb{0}, rw{0}, rm{0}, variant{0};
     TileHint load() const {
         TileHint h;
         h.threads = threads.load(std::memory_order_relaxed);
@@ -18,10 +26,15 @@ struct HintSlot {
         h.smem_kb = smem_kb.load(std::memory_order_relaxed);
         h.rw = rw.load(std::memory_order_relaxed);
         h.rm = rm.load(std::memory_order_relaxed);
+        h.variant = variant.load(std::memory_order_relaxed);
         return h;
     }
 };
 HintSlot g_hints[3];
+TileHint current_hint(int op) { return g_hints[op].load(); }
+#else
+TileHint current_hint(int) { return TileHint(); }
+#endif
 std::atomic<unsigned long long> g_launches{0};
 
 
@@ -51,6 +64,26 @@ int make_col_geom(int K, int P, int Co, Geom* g) {
 
 namespace adder {
 void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
+
+int ensure_dynamic_smem(const void* kernel, size_t bytes) {
+    static std::mutex mu;
+    static std::map<std::pair<const void*, int>, size_t> granted;     // (kernel, device) -> bytes opted in
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return ADDER_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = granted.find({kernel, dev});
+    if (it == granted.end()) {
+        int optin = 0;
+        if (cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess || optin <= 0)
+            return ADDER_ERR_CUDA;
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, optin) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return ADDER_ERR_CUDA;
+        }
+        it = granted.emplace(std::make_pair(kernel, dev), (size_t)optin).first;
+    }
+    return bytes <= it->second ? ADDER_OK : ADDER_ERR_UNSUPPORTED;
+}
 }  // namespace adder
 
 extern "C" {
@@ -90,7 +123,7 @@ int adder_b200_forward(const float* x, const float* w, float* out, int n, int ci
     if (st != ADDER_OK) return st;
     if (n == 0) return ADDER_OK;
     if (x == nullptr || w == nullptr || out == nullptr) return ADDER_ERR_NULL_POINTER;
-    return launch_fwd(g, x, w, out, g_hints[0].load(), static_cast<cudaStream_t>(stream));
+    return launch_fwd(g, x, w, out, current_hint(0), static_cast<cudaStream_t>(stream));
 }
 
 int adder_b200_backward_input(const float* grad_out, const float* x, const float* w, float* grad_x, int n, int ci,
@@ -101,14 +134,14 @@ int adder_b200_backward_input(const float* grad_out, const float* x, const float
     if (n == 0) return ADDER_OK;
     if (grad_out == nullptr || x == nullptr || w == nullptr || grad_x == nullptr) return ADDER_ERR_NULL_POINTER;
     return launch_gx(g, grad_out, x, w, grad_x, (flags & ADDER_FLAG_FAST_CLAMP) != 0,
-                     (flags & ADDER_FLAG_ACCUMULATE) != 0, g_hints[1].load(), static_cast<cudaStream_t>(stream));
+                     (flags & ADDER_FLAG_ACCUMULATE) != 0, current_hint(1), static_cast<cudaStream_t>(stream));
 }
 
 size_t adder_b200_backward_weight_workspace_bytes(int n, int ci, int h, int wd, int co, int k, int stride, int pad) {
     Geom g;
     if (make_geom(n, ci, h, wd, co, k, stride, pad, &g) != ADDER_OK) return 0;
     if (n == 0) g.N = 1;
-    return gw_workspace_bytes(g, g_hints[2].load());
+    return gw_workspace_bytes(g, current_hint(2));
 }
 
 int adder_b200_backward_weight(const float* grad_out, const float* x, const float* w, float* grad_w, float eta,
@@ -121,7 +154,7 @@ int adder_b200_backward_weight(const float* grad_out, const float* x, const floa
     if (n > 0 && (grad_out == nullptr || x == nullptr)) return ADDER_ERR_NULL_POINTER;
     // An empty batch still defines the gradient (all zeros); the kernels handle N = 0 tiles.
     return launch_gw(g, grad_out, x, w, grad_w, eta, out_norm, (flags & ADDER_FLAG_ACCUMULATE) != 0, workspace,
-                     workspace_bytes, g_hints[2].load(), static_cast<cudaStream_t>(stream));
+                     workspace_bytes, current_hint(2), static_cast<cudaStream_t>(stream));
 }
 
 int adder_b200_backward(const float* grad_out, const float* x, const float* w, float* grad_x, float* grad_w,
@@ -139,13 +172,13 @@ int adder_b200_conv_col(const float* x, const float* w, float* y, int K, int P, 
     if (st != ADDER_OK) return st;
     if (P == 0) return ADDER_OK;
     if (x == nullptr || w == nullptr || y == nullptr) return ADDER_ERR_NULL_POINTER;
-    return launch_fwd(g, x, w, y, g_hints[0].load(), static_cast<cudaStream_t>(stream));
+    return launch_fwd(g, x, w, y, current_hint(0), static_cast<cudaStream_t>(stream));
 }
 
 size_t adder_b200_col_workspace_bytes(int K, int P, int Co) {
     Geom g;
     if (make_col_geom(K, P, Co, &g) != ADDER_OK) return 0;
-    return gw_workspace_bytes(g, g_hints[2].load());
+    return gw_workspace_bytes(g, current_hint(2));
 }
 
 int adder_b200_conv_weight_col(const float* grad_y, const float* x, const float* w, float* grad_w, int K, int P,
@@ -155,7 +188,7 @@ int adder_b200_conv_weight_col(const float* grad_y, const float* x, const float*
     if (st != ADDER_OK) return st;
     if (P == 0) return ADDER_OK;   // accumulating nothing
     if (grad_y == nullptr || x == nullptr || w == nullptr || grad_w == nullptr) return ADDER_ERR_NULL_POINTER;
-    return launch_gw(g, grad_y, x, w, grad_w, 0.f, nullptr, 1, workspace, workspace_bytes, g_hints[2].load(),
+    return launch_gw(g, grad_y, x, w, grad_w, 0.f, nullptr, 1, workspace, workspace_bytes, current_hint(2),
                      static_cast<cudaStream_t>(stream));
 }
 
@@ -166,7 +199,7 @@ int adder_b200_conv_input_col(const float* grad_y, const float* x, const float* 
     if (st != ADDER_OK) return st;
     if (P == 0) return ADDER_OK;
     if (grad_y == nullptr || x == nullptr || w == nullptr || grad_i == nullptr) return ADDER_ERR_NULL_POINTER;
-    return launch_gx(g, grad_y, x, w, grad_i, 0, 1, g_hints[1].load(), static_cast<cudaStream_t>(stream));
+    return launch_gx(g, grad_y, x, w, grad_i, 0, 1, current_hint(1), static_cast<cudaStream_t>(stream));
 }
 
 int adder_b200_backward_col(const float* grad_y, const float* x, const float* w, float* grad_w, float* grad_i,
@@ -183,12 +216,13 @@ int adder_b200_describe_plan(int op, int n, int ci, int h, int wd, int co, int k
     const int st = make_geom(n, ci, h, wd, co, k, stride, pad, &g);
     if (st != ADDER_OK) return st;
     buf[0] = 0;
-    if (op == 0) return describe_fwd(g, g_hints[0].load(), buf, buf_bytes);
-    if (op == 1) return describe_gx(g, (flags & ADDER_FLAG_FAST_CLAMP) != 0, g_hints[1].load(), buf, buf_bytes);
-    if (op == 2) return describe_gw(g, g_hints[2].load(), buf, buf_bytes);
+    if (op == 0) return describe_fwd(g, current_hint(0), buf, buf_bytes);
+    if (op == 1) return describe_gx(g, (flags & ADDER_FLAG_FAST_CLAMP) != 0, current_hint(1), buf, buf_bytes);
+    if (op == 2) return describe_gw(g, current_hint(2), buf, buf_bytes);
     return ADDER_ERR_BAD_SHAPE;
 }
 
+#ifdef ADDER_B200_TUNING
 int adder_b200_set_tile_hint(int op, int threads, int channel_groups, int tile_rows, int tile_images,
                              int chunk_channels, int smem_kb) {
     if (op < 0 || op > 2) return ADDER_ERR_BAD_SHAPE;
@@ -198,11 +232,18 @@ int adder_b200_set_tile_hint(int op, int threads, int channel_groups, int tile_r
     return ADDER_OK;
 }
 
+int adder_b200_set_variant(int op, int variant) {
+    if (op < 0 || op > 2 || variant < 0 || variant > 1) return ADDER_ERR_BAD_SHAPE;
+    g_hints[op].variant.store(variant);
+    return ADDER_OK;
+}
+
 int adder_b200_set_micro_tile(int op, int pixels_per_thread, int channels_per_thread) {
     if (op < 0 || op > 2) return ADDER_ERR_BAD_SHAPE;
     g_hints[op].rw.store(pixels_per_thread);
     g_hints[op].rm.store(channels_per_thread);
     return ADDER_OK;
 }
+#endif  // ADDER_B200_TUNING
 
 }  // extern "C"

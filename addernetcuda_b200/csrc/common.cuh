@@ -68,6 +68,11 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
     return r;
 }
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
 __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
     uint64_t r;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
@@ -94,6 +99,24 @@ __device__ __forceinline__ void load_run(float (&dst)[N], const float* __restric
     } else {
 #pragma unroll
         for (int i = 0; i < N; ++i) dst[i] = src[i];
+    }
+}
+
+// Loads N consecutive (v, v) pairs (2N floats of a row stored with every value doubled) into 64-bit
+// registers.  When ALIGNED the address is a multiple of 16 bytes: 128-bit loads, two pairs each;
+// otherwise the address is still a multiple of 8 bytes (doubled rows start pairs on even words).
+template <int N, bool ALIGNED>
+__device__ __forceinline__ void load_pairs(uint64_t (&dst)[N], const float* __restrict__ src) {
+    if (ALIGNED) {
+#pragma unroll
+        for (int i = 0; i + 2 <= N; i += 2) {
+            const ulonglong2 v = *reinterpret_cast<const ulonglong2*>(src + 2 * i);
+            dst[i] = v.x; dst[i + 1] = v.y;
+        }
+        if (N % 2 == 1) dst[N - 1] = *reinterpret_cast<const unsigned long long*>(src + 2 * (N - 1));
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) dst[i] = *reinterpret_cast<const unsigned long long*>(src + 2 * i);
     }
 }
 

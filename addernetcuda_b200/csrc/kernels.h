@@ -18,7 +18,8 @@ struct TileHint {
     int smem_kb = 0;   // shared-memory budget per CTA
     int rw = 0;        // pixels per thread segment (register tile width)
     int rm = 0;        // channels per thread (register tile height)
-    bool is_default() const { return !(threads | cg | th | ti | ck | smem_kb | rw | rm); }
+    int variant = 0;   // 0 = choose the kernel family automatically, 1 = the non-persistent kernels
+    bool is_default() const { return !(threads | cg | th | ti | ck | smem_kb | rw | rm | variant); }
 };
 
 struct FwdArgs {
@@ -87,9 +88,22 @@ inline int launched(int n = 1) {
     return ADDER_OK;
 }
 
+// Opt a kernel in to `bytes` of dynamic shared memory.  The attribute is set once per (kernel, device), to
+// the device's opt-in maximum, and remembered; later calls cost a lock and a table lookup.
+int ensure_dynamic_smem(const void* kernel, size_t bytes);
+
 int launch_fwd(const Geom& g, const float* x, const float* w, float* out, const TileHint& hint, cudaStream_t s);
+// Persistent multi-stage forward (adder_fwd_pipe.cu)
+bool fwd_pipe_applicable(const Geom& g, const TileHint& hint);
+int launch_fwd_pipe(const Geom& g, const float* x, const float* w, float* out, const TileHint& hint, cudaStream_t s);
+int describe_fwd_pipe(const Geom& g, const TileHint& hint, char* buf, size_t n);
 int launch_gx(const Geom& g, const float* gout, const float* x, const float* w, float* gx, int fast,
               int accumulate, const TileHint& hint, cudaStream_t s);
+// Persistent multi-stage input gradient of stride-1 layers (adder_bwd_input_pipe.cu)
+bool gx_pipe_applicable(const Geom& g, const TileHint& hint);
+int launch_gx_pipe(const Geom& g, const float* gout, const float* x, const float* w, float* gx, int fast,
+                   int accumulate, const TileHint& hint, cudaStream_t s);
+int describe_gx_pipe(const Geom& g, int fast, const TileHint& hint, char* buf, size_t n);
 size_t gw_workspace_bytes(const Geom& g, const TileHint& hint);
 int launch_gw(const Geom& g, const float* gout, const float* x, const float* w, float* gw, float eta,
               float* out_norm, int accumulate, void* workspace, size_t workspace_bytes, const TileHint& hint,
@@ -104,6 +118,13 @@ int launch_pointwise_gx(const Geom& g, const float* gout, const float* x, const 
 int pointwise_gw_splits(const Geom& g);
 int launch_pointwise_gw(const Geom& g, const float* gout, const float* x, float* part, float* gsum_part,
                         unsigned int* ticket, int splits, cudaStream_t stream);
+
+// Warp-tile weight gradient with row-range scheduling (adder_bwd_weight_pipe.cu)
+bool gw_pipe_applicable(const Geom& g, const TileHint& hint);
+int gw_pipe_splits(const Geom& g, const TileHint& hint);
+int launch_gw_pipe(const Geom& g, const float* gout, const float* x, float* part, float* gsum_part,
+                   unsigned int* ticket, int splits, const TileHint& hint, cudaStream_t stream);
+int describe_gw_pipe(const Geom& g, const TileHint& hint, char* buf, size_t n);
 
 bool gw1x1_applicable(const Geom& g);
 int gw1x1_splits(const Geom& g);

@@ -170,16 +170,25 @@ ADDER_API int adder_b200_batchnorm_backward(const float* dz, const float* y, con
                                             float* dresidual, float* dgamma, float* dbeta, int relu, void* workspace,
                                             size_t workspace_bytes, int n, int c, int hw, void* stream);
 
-/* ---- tuning hook ---------------------------------------------------------------------------
- * Overrides the tile heuristics of one kernel family for subsequent calls from any thread
- * (op: 0 forward, 1 input gradient, 2 weight gradient; a value of 0 restores the automatic
- * choice).  Meant for parameter sweeps; not needed for normal use.  No reference counterpart. */
+#ifdef ADDER_B200_TUNING
+/* ---- tuning build only (libadder_b200_tuning.so, compiled with -DADDER_B200_TUNING) ---------------
+ * The product library exports none of these and keeps no tile state: any thread calling a setter would
+ * change every other thread's kernels.  Parameter sweeps and the tests that must reach a particular
+ * kernel variant load the tuning library instead.  No reference counterpart. */
+
+/* Overrides the tile heuristics of one kernel family for subsequent calls from any thread
+ * (op: 0 forward, 1 input gradient, 2 weight gradient; a value of 0 restores the automatic choice). */
 ADDER_API int adder_b200_set_tile_hint(int op, int threads, int channel_groups, int tile_rows, int tile_images,
                              int chunk_channels, int smem_kb);
 
 /* Overrides the per-thread register tile of one kernel family (pixels per thread segment: 4, 7 or 8;
- * channels per thread: 4 or 8; 0,0 restores the automatic choice).  Tuning only. */
+ * channels per thread: 4 or 8; 0,0 restores the automatic choice). */
 ADDER_API int adder_b200_set_micro_tile(int op, int pixels_per_thread, int channels_per_thread);
+
+/* Kernel family of one op: 0 = automatic (persistent multi-stage kernels where they apply),
+ * 1 = the non-persistent kernels everywhere. */
+ADDER_API int adder_b200_set_variant(int op, int variant);
+#endif /* ADDER_B200_TUNING */
 
 /* Writes a one-line description of the tile plan the library would use for this layer on the
  * current device (op: 0 forward, 1 input gradient, 2 weight gradient) into buf (NUL-terminated,

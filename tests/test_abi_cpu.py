@@ -15,18 +15,35 @@ REFERENCE_DIR = os.environ.get("ADDERNET_REFERENCE_DIR") or str(ROOT / "baseline
 
 
 def _declared():
+    """(entry points of the product library, entry points only the tuning build adds), from the header."""
     text = (ROOT / "include" / "adder_b200.h").read_text()
-    return sorted(set(re.findall(r"ADDER_API\s+[\w\s\*]+?\b(adder_b200_\w+)\s*\(", text)))
+    pat = r"ADDER_API\s+[\w\s\*]+?\b(adder_b200_\w+)\s*\("
+    m = re.search(r"#ifdef ADDER_B200_TUNING(.*?)#endif /\* ADDER_B200_TUNING \*/", text, re.S)
+    tuning = sorted(set(re.findall(pat, m.group(1))))
+    product = sorted(set(re.findall(pat, text.replace(m.group(0), ""))))
+    return product, tuning
 
 
 def test_library_exports_every_declared_symbol():
     from addernetcuda_b200 import _lib
     lib = _lib.load()
-    names = _declared()
-    assert len(names) >= 14
+    names, tuning_names = _declared()
+    assert len(names) >= 14 and len(tuning_names) == 3
     for n in names:
         assert hasattr(lib, n), f"{n} declared in the header but not exported"
     assert sorted(_lib.SIGNATURES.keys()) == names, "ctypes prototypes and header disagree"
+    assert sorted(_lib.TUNING_SIGNATURES.keys()) == tuning_names
+    # the product library has no tile-override entry points (no process-wide mutable tile state) ...
+    for n in tuning_names:
+        assert not hasattr(lib, n), f"{n} must not be exported by the product library"
+    # ... the tuning library has them, on top of everything else
+    with _lib.tuning() as tlib:
+        for n in names + tuning_names:
+            assert hasattr(tlib, n), n
+        assert tlib.adder_b200_set_tile_hint(7, 0, 0, 0, 0, 0, 0) == 2
+        assert tlib.adder_b200_set_variant(0, 1) == 0
+        assert "persistent" not in _lib.describe_plan(0, 256, 16, 32, 32, 16, 3, 1, 1, 0)
+    assert "persistent" in _lib.describe_plan(0, 256, 16, 32, 32, 16, 3, 1, 1, 0)     # overrides cleared on exit
 
 
 def test_version_and_status_strings():
@@ -53,7 +70,6 @@ def test_output_size_and_shape_errors():
     assert lib.adder_b200_forward(None, None, None, 0, 4, 8, 8, 4, 3, 1, 1, None) == 0     # empty batch: no-op
     assert lib.adder_b200_backward_weight_workspace_bytes(256, 16, 32, 32, 16, 3, 1, 1) > 0
     assert lib.adder_b200_backward_weight_workspace_bytes(256, 16, 32, 32, 16, 4, 1, 1) == 0
-    assert lib.adder_b200_set_tile_hint(7, 0, 0, 0, 0, 0, 0) == 2
 
 
 def test_cpu_tensors_are_rejected_not_computed():

@@ -111,20 +111,40 @@ def test_every_register_tile(name, tile, golden, ac):
     that all compiled variants are checked on small cases too."""
     from addernetcuda_b200 import _lib
     from tests.cases import LAYER_BY_NAME
-    lib = _lib.load()
     case = LAYER_BY_NAME[name]
     x, w, g = (_gpu(a) for a in draw_layer(case))
     s, p = case["stride"], case["pad"]
-    try:
-        assert lib.adder_b200_set_micro_tile(0, tile[0], tile[1]) == 0
-        assert lib.adder_b200_set_micro_tile(1, tile[0], 4) == 0
-        _assert(golden.check(name, "out", ac.forward(x, w, s, p)))
-        _assert(golden.check(name, "grad_x", ac.backward_input(g, x, w, s, p)))
-        _assert(golden.check(name, "grad_x", ac.backward_input(g, x, w, s, p, fast_clamp=True)))
-    finally:
-        lib.adder_b200_set_micro_tile(0, 0, 0)
-        lib.adder_b200_set_micro_tile(1, 0, 0)
-        lib.adder_b200_set_tile_hint(2, 0, 0, 0, 0, 0, 0)
+    with _lib.tuning() as lib:
+        for variant in (0, 1):          # the persistent kernels where they apply, then the non-persistent ones
+            for op in range(3):
+                assert lib.adder_b200_set_variant(op, variant) == 0
+            assert lib.adder_b200_set_micro_tile(0, tile[0], tile[1]) == 0
+            assert lib.adder_b200_set_micro_tile(1, tile[0], 4) == 0
+            _assert(golden.check(name, "out", ac.forward(x, w, s, p)))
+            _assert(golden.check(name, "grad_x", ac.backward_input(g, x, w, s, p)))
+            _assert(golden.check(name, "grad_x", ac.backward_input(g, x, w, s, p, fast_clamp=True)))
+
+
+@pytest.mark.parametrize("case", [c for c in LAYER_CASES if c["name"].startswith(("cfg1", "r20", "r50_n1_c64to64", "r50_n2_c64to256"))],
+                         ids=lambda c: c["name"])
+def test_non_persistent_kernels_match_reference_outputs(case, golden, ac):
+    """The layers that take the persistent kernels by default, through the non-persistent ones (which
+    remain the path of every geometry the persistent kernels do not cover)."""
+    from addernetcuda_b200 import _lib
+    x, w, g = (_gpu(a) for a in draw_layer(case))
+    s, p = case["stride"], case["pad"]
+    with _lib.tuning() as lib:
+        for op in range(3):
+            assert lib.adder_b200_set_variant(op, 1) == 0
+        for op in range(3):
+            assert "persistent" not in _lib.describe_plan(op, case["n"], case["ci"], case["h"], case["w"], case["co"],
+                                                          case["k"], s, p, 1)
+            assert "warp-tile" not in _lib.describe_plan(op, case["n"], case["ci"], case["h"], case["w"], case["co"],
+                                                         case["k"], s, p, 1)
+        _assert(golden.check(case["name"], "out", ac.forward(x, w, s, p)))
+        _assert(golden.check(case["name"], "grad_x", ac.backward_input(g, x, w, s, p)))
+        _assert(golden.check(case["name"], "grad_x", ac.backward_input(g, x, w, s, p, fast_clamp=True)))
+        _assert(golden.check(case["name"], "grad_w", ac.backward_weight(g, x, w, s, p)))
 
 
 def test_module_autograd_and_bias(ac):
@@ -278,19 +298,15 @@ def test_pointwise_stride2_kernels(geom, ac):
         assert lib.adder_b200_backward_input(*args, flags | _lib.FLAG_ACCUMULATE, stream) == 0
         _assert(O.compare("accumulated", acc, (base + gx).cpu()))
         assert torch.equal(acc[:, :, ~mask], base[:, :, ~mask])
-    try:    # the tiled kernels on the same inputs
-        assert lib.adder_b200_set_micro_tile(0, 8, 4) == 0
-        assert lib.adder_b200_set_micro_tile(1, 4, 4) == 0
+    with _lib.tuning() as tlib:    # the tiled kernels on the same inputs
+        assert tlib.adder_b200_set_micro_tile(0, 8, 4) == 0
+        assert tlib.adder_b200_set_micro_tile(1, 4, 4) == 0
         assert "pointwise" not in _lib.describe_plan(0, n, ci, h, w_, co, 1, 2, 0, 0)
         _assert(O.compare("tiled out", ac.forward(xg, wg, 2, 0), out.cpu()))
         _assert(O.compare("tiled grad_x", ac.backward_input(gg, xg, wg, 2, 0, fast_clamp=True), want_gx))
-        assert lib.adder_b200_set_tile_hint(2, 256, 0, 0, 0, 0, 0) == 0
+        assert tlib.adder_b200_set_tile_hint(2, 256, 0, 0, 0, 0, 0) == 0
         assert "pointwise=0" in _lib.describe_plan(2, n, ci, h, w_, co, 1, 2, 0, 0)
         _assert(O.compare("tiled grad_w", ac.backward_weight(gg, xg, wg, 2, 0), want_gws))
-    finally:
-        lib.adder_b200_set_micro_tile(0, 0, 0)
-        lib.adder_b200_set_micro_tile(1, 0, 0)
-        lib.adder_b200_set_tile_hint(2, 0, 0, 0, 0, 0, 0)
 
 
 @pytest.mark.parametrize("geom", [(3, 16, 32, 32, 32), (5, 32, 64, 16, 16), (2, 6, 5, 12, 24), (2, 6, 5, 12, 20), (2, 9, 3, 10, 7)],
@@ -318,10 +334,8 @@ def test_stride2_paired_input_gradient(geom, ac):
         got = ac.backward_input(gg, xg, wg, 2, 1, fast_clamp=fast)
         _assert(O.compare("paired grad_x fast=%d" % fast, got, want_gx))
         results.append(got)
-    try:
-        assert lib.adder_b200_set_tile_hint(1, 256, 0, 0, 0, 0, 0) == 0
+    with _lib.tuning() as tlib:
+        assert tlib.adder_b200_set_tile_hint(1, 256, 0, 0, 0, 0, 0) == 0
         assert "segs/thread=1" in _lib.describe_plan(1, n, ci, h, w_, co, 3, 2, 1, 1)
         for fast in (False, True):
             _assert(O.compare("one-class grad_x fast=%d" % fast, ac.backward_input(gg, xg, wg, 2, 1, fast_clamp=fast), want_gx))
-    finally:
-        lib.adder_b200_set_tile_hint(1, 0, 0, 0, 0, 0, 0)
