@@ -255,6 +255,17 @@ static GwPipePlan plan_gw_pipe_t(const Geom& g, const TileHint& hint) {
             else break;
         }
     }
+    if (hint.cg <= 0) {
+        // Every CTA writes its whole block of the gradient as a slice of partial sums, and the finishing
+        // kernel reads them all back: keep that traffic small next to the layer's work (6 MB, or 4 bytes per
+        // 500 multiply-adds for the big layers) by shrinking the block, which trades it for more staging.
+        const double triples = (double)g.N * g.Ho * g.Wo * g.Co * g.Ci * KS * KS;
+        double cap = triples / 500.0 * 4.0;
+        if (cap < 6.0 * 1024 * 1024) cap = 6.0 * 1024 * 1024;
+        while (oto * oti > 1 && 2.0 * sms * (256.0 * oto * oti * KS * KS) * 4.0 > cap) {
+            if (oto >= oti) oto /= 2; else oti /= 2;
+        }
+    }
     if (oto > tiles_o || oti > tiles_i || tiles_o % oto || tiles_i % oti || GWP_WARPS % (oto * oti)) {
         p.status = ADDER_ERR_INTERNAL; return p;
     }
