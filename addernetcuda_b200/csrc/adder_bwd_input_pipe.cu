@@ -420,7 +420,7 @@ static GxPipePlan plan_gx_pipe_kg(const Geom& g, const TileHint& hint, int kg_fo
     a.red_floats = a.KG > 1 ? (a.KG - 1) * RC * RW * group : 0;
     // output channels per chunk: a multiple of the group count; three stages within the budget.  The sums
     // of a multi-chunk unit go through per-thread totals in shared memory.
-    const int budget_floats = (hint.smem_kb > 0 ? hint.smem_kb : 100) * 1024 / 4 - a.red_floats - a.g1_size;
+    const int budget_floats = (hint.smem_kb > 0 ? hint.smem_kb : 108) * 1024 / 4 - a.red_floats - a.g1_size;
     int cko = 16 > a.KG ? 16 : a.KG;
     if (cko > g.Co) cko = g.Co;
     const bool long_sum = (long long)g.Co * KS * KS > 1024;

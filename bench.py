@@ -48,10 +48,13 @@ RESNET20_LAYERS = [
 ]
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch, 16->16 32x32 k3 layer at batch 256 (ncu --set full)
-NCU_DRAM_BYTES = {"adder_fwd_kernel": 16816384, "adder_gx_kernel": 33628160, "adder_gw_kernel": 33596672}
-# 4*(|x|+|w|+|out|), 4*(|g|+|x|+|w|+|gx|), 4*(|g|+|x|+|w|+|gw|) for that layer
-ALGO_BYTES_16x16 = {"adder_fwd_kernel": 33563648, "adder_gx_kernel": 50340864, "adder_gw_kernel": 33572864}
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of each adder kernel on the 16->16 32x32 k3
+# layer at batch 256 (ncu capture summarised in profiles/adder_kernels_c16to16_32x32_b256.txt), and the
+# algorithmic bytes of that launch: 4(|x|+|w|+|out|), 4(|g|+|x|+|w|+|gx|), 4(|g|+|x|+|w|+|gw|).
+NCU_CAPTURE = "profiles/adder_kernels_c16to16_32x32_b256.txt"
+NCU_DRAM_BYTES = {"fwd": 16816384, "grad_x": 33628160, "grad_w": 33596672}
+ALGO_BYTES_16x16 = {"fwd": 33563648, "grad_x": 50340864, "grad_w": 33572864}
+KERNEL_NAMES = {"fwd": "adder_fwd_pipe_kernel", "grad_x": "adder_gx_pipe_kernel", "grad_w": "adder_gw_pipe_kernel"}
 
 
 def triples(n, shape):
@@ -117,7 +120,7 @@ def cpu_step_factory(batch: int, seed: int = 1434):
     import torch
     from addernetcuda_b200 import resnet as R
     from oracle import adder_unfold as U
-    from tests.cases import resnet20_batch
+    from addernetcuda_b200.synthetic import resnet20_batch
     torch.set_num_threads(os.cpu_count() or 1)
     net = R.resnet20(conv=U.adder2d)
     R.init_seeded(net, seed)
@@ -177,10 +180,11 @@ def run_reference_arm(args):
 
 # ------------------------------------------------------------------------------------------ GPU arm
 
-def time_layer_ops(n, shape, iters=5, inner=4):
+def time_layer_ops(n, shape, iters=9):
     """Device time (ms) of the three adder kernels of one layer, and of the two gradient kernels issued
-    together as the layer's backward does, CUDA events on the current stream around a CUDA-graph
-    replay of `inner` launches, L2 flushed before every replay."""
+    together as the layer's backward does.  Every sample is ONE launch (a CUDA-graph replay, so that the
+    host is out of the picture) between CUDA events on the current stream, with L2 flushed (a 256 MB
+    write) before it: cold-cache numbers.  Median of `iters` samples."""
     import torch
     from addernetcuda_b200 import adder_cuda as ac
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -206,17 +210,169 @@ def time_layer_ops(n, shape, iters=5, inner=4):
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            for _ in range(inner):
-                f()
+            f()
         ts = []
         for _ in range(iters):
             flush.zero_()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(); graph.replay(); b.record()
             torch.cuda.synchronize()
-            ts.append(a.elapsed_time(b) / inner)
+            ts.append(a.elapsed_time(b))
         out[name] = statistics.median(ts)
     return out
+
+
+# ------------------------------------------------------------------------------------------ the reference's kernels
+
+def load_reference_cuda():
+    """The reference's own adder.py on top of its own CUDA extension, both as installed (unmodified apart
+    from four `x.type()` -> `x.scalar_type()` tokens the current PyTorch needs to compile it) in
+    baseline/_ref/ by baseline/install_ref.py.  Returns the module, or None with the reason."""
+    import importlib.util
+    ref = ROOT / "baseline" / "_ref"
+    so = sorted(ref.glob("adder_cuda*.so"))
+    if not so or not (ref / "adder.py").exists():
+        return None, "baseline/_ref holds no reference build (run baseline/install_ref.py where the reference checkout is)"
+    saved = sys.modules.get("adder_cuda")
+    try:
+        spec = importlib.util.spec_from_file_location("adder_cuda", so[0])
+        ext = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(ext)
+        sys.modules["adder_cuda"] = ext               # adder.py does `import adder_cuda`
+        spec = importlib.util.spec_from_file_location("reference_adder", ref / "adder.py")
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        return mod, None
+    except Exception as e:  # noqa: BLE001  (an extension that does not load is reported, not fatal)
+        return None, f"reference extension did not load: {e!r}"[:200]
+    finally:
+        if saved is not None:
+            sys.modules["adder_cuda"] = saved
+        else:
+            sys.modules.pop("adder_cuda", None)
+
+
+def reference_cuda_in_bounds(n, shape):
+    """The reference kernels guard nothing beyond their launch-time divisibility test: CONV needs K, Co and
+    P in multiples of 16 to stay inside its buffers, CONV_BACKWARD in multiples of 8 (adder.cu:19-70,
+    :194-272).  Only such shapes are ever handed to it."""
+    ci, co, h, w, s, k, p = shape
+    ho, wo = (h - k + 2 * p) // s + 1, (w - k + 2 * p) // s + 1
+    K, P = ci * k * k, n * ho * wo
+    return K % 16 == 0 and co % 16 == 0 and P % 16 == 0
+
+
+def time_reference_cuda(ref_adder, n, shape, iters=3):
+    """fwd and bwd device time (ms) of one layer through the reference's adder2d_function (F.unfold, permute
+    copies, its CONV / CONV_BACKWARD kernels, col2im, the rescale): the path its README profiles."""
+    import torch
+    dev = torch.device("cuda", torch.cuda.current_device())
+    ci, co, h, w, s, k, p = shape
+    ho, wo = (h - k + 2 * p) // s + 1, (w - k + 2 * p) // s + 1
+    x = torch.randn(n, ci, h, w, device=dev, requires_grad=True)
+    wt = (torch.randn(co, ci, k, k, device=dev) * math.sqrt(2.0 / (ci * k * k))).requires_grad_()
+    g = torch.randn(n, co, ho, wo, device=dev)
+    tf, tb = [], []
+    for i in range(iters + 1):
+        x.grad = wt.grad = None
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        torch.cuda.synchronize()
+        e[0].record()
+        y = ref_adder.adder2d_function(x, wt, s, p)
+        e[1].record()
+        y.backward(g)
+        e[2].record()
+        torch.cuda.synchronize()
+        if i > 0:
+            tf.append(e[0].elapsed_time(e[1])); tb.append(e[1].elapsed_time(e[2]))
+    return statistics.median(tf), statistics.median(tb)
+
+
+# ------------------------------------------------------------------------------------------ CPU timings of single layers
+
+def time_layer_cpu(n, shape, iters=3):
+    """fwd+bwd seconds of one adder2d layer on the host through the port of the reference's adder.py (unfold,
+    column matrices, rescale), all host threads; 1 warm-up + `iters` timed runs, median."""
+    import torch
+    from oracle import adder_unfold as U
+    torch.set_num_threads(os.cpu_count() or 1)
+    ci, co, h, w, s, k, p = shape
+    ho, wo = (h - k + 2 * p) // s + 1, (w - k + 2 * p) // s + 1
+    gen = torch.Generator().manual_seed(1234 + 100)
+    x = torch.randn((n, ci, h, w), generator=gen).requires_grad_()
+    wt = (torch.randn((co, ci, k, k), generator=gen) * math.sqrt(2.0 / (ci * k * k))).requires_grad_()
+    g = torch.randn((n, co, ho, wo), generator=gen)
+    ts = []
+    for i in range(iters + 1):
+        x.grad = wt.grad = None
+        t0 = time.perf_counter()
+        U.adder2d_function(x, wt, s, p).backward(g)
+        if i > 0:
+            ts.append(time.perf_counter() - t0)
+    return statistics.median(ts)
+
+
+def resnet50_block(dev, fp32_peak):
+    """ResNet-50 adder training step at batch 64 (224x224 synthetic images, 1000 classes, fp32, SGD momentum):
+    ms per step over a few CUDA-graph replays, and how much of it the adder kernels are."""
+    import numpy as np
+    import torch
+    from addernetcuda_b200 import resnet as R
+    from addernetcuda_b200.synthetic import image_batch
+    from addernetcuda_b200.train import TrainStep
+    B = 64
+    net = R.resnet50()
+    R.init_seeded(net, 1434)
+    net = net.to(dev).train()
+    ts = TrainStep(net, (B, 3, 224, 224), 1000, lr=0.1, momentum=0.9, use_graph=True, device=dev)
+    images, labels = image_batch(B, 224, 1000, 1434)
+    ts.load_batch(torch.from_numpy(images).to(dev), torch.from_numpy(labels).to(dev))
+    for _ in range(2):
+        ts.run()
+    torch.cuda.synchronize()
+    K = 5
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        ts.run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / K
+    out = {"workload": "resnet50_adder_train_step_fp32", "per_gpu_batch": B, "steps": K, "ms_per_step": ms,
+           "images_per_s": B / (ms * 1e-3), "final_loss": float(ts.loss)}
+    T = resnet50_triples(B)
+    out["adder_triples_per_forward"] = T
+    if fp32_peak:
+        # the whole step against the roofline of its adder work alone (9 ops per triple): a lower bound on
+        # what the adder kernels reach, since the step also holds BatchNorm, the stem and the optimiser
+        out["step_pct_fp32_peak_lower_bound"] = 100 * 9 * T / (ms * 1e-3) / fp32_peak
+    del ts, net
+    torch.cuda.empty_cache()
+    return out
+
+
+def resnet50_triples(batch):
+    """(co, k, pixel) triples of the 52 adder layers of ResNet-50 in one forward pass at 224x224."""
+    import torch
+    from addernetcuda_b200 import resnet as R, adder as A
+    total = [0]
+    orig = A.adder2d.forward
+
+    def fwd(self, x):
+        n, c, h, w = x.shape
+        k, s, p = self.kernel_size, self.stride, self.padding
+        ho, wo = (h - k + 2 * p) // s + 1, (w - k + 2 * p) // s + 1
+        total[0] += n * ho * wo * self.output_channel * c * k * k
+        return x.new_empty((n, self.output_channel, ho, wo))
+
+    A.adder2d.forward = fwd
+    try:
+        with torch.device("meta"):
+            net = R.resnet50(fused_bn=False)
+            net(torch.empty(batch, 3, 224, 224))
+    finally:
+        A.adder2d.forward = orig
+    return total[0]
 
 
 def run_gpu_arm(args):
@@ -334,7 +490,7 @@ def run_gpu_arm(args):
                        "optimizer": "sgd(lr=0.1,momentum=0.9)", "cuda_graph": not args.no_graph,
                        "input_grad_clamp": "exact" if args.exact_clamp else "saturating-add form",
                        "batchnorm": "sync" if (args.sync_bn and world > 1) else "per-rank",
-                       "parallelism": f"dp{world}", "bucket_mb": args.bucket_mb,
+                       "parallelism": f"dp{world}", "buckets": len(ddp.buckets) if ddp is not None else 0,
                        "l2": "not flushed between steps: one step streams far more than the 126 MB L2"},
             "e2e": {"value": world * B * K / (ms_e2e * 1e-3), "unit": "images/s", "ms_per_step": ms_e2e / K,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -363,29 +519,36 @@ def run_gpu_arm(args):
             for k in tot:
                 tot[k] += t[k] * mult
         dom = max(("fwd", "grad_x", "grad_w"), key=tot.get)
-        dom_kernel = {"fwd": "adder_fwd_kernel", "grad_x": "adder_gx_kernel", "grad_w": "adder_gw_kernel"}[dom]
         achieved = 3 * tot_T / (tot[dom] * 1e-3)
         all_ms = tot["fwd"] + tot["grad_x"] + tot["grad_w"]
         pass_ms = tot["fwd"] + tot["bwd"]
-        # algorithmic bytes of the dominant kernel over the layer set (inputs + outputs once)
         line["roofline"] = {
-            "bound": "fp32", "kernel": dom_kernel,
+            "bound": "fp32", "kernel": KERNEL_NAMES[dom],
             "achieved": achieved / 1e12, "peak": fp32_peak / 1e12, "unit": "TFLOP/s", "frac": achieved / fp32_peak,
             "peak_source": f"2*128*{sms} SMs*{f_max:.0f} MHz (FP32 CUDA-core FMA peak; MEASURED_PEAKS.json holds no SIMT figure)",
             "ops_rule": "3 ops per (co,k,pixel) triple per pass", "launches": 20, "ms_total": tot[dom],
-            "traffic": NCU_DRAM_BYTES.get(dom_kernel),
-            "traffic_note": "dram read+write bytes of ONE launch on the 16->16 32x32 layer at batch 256 from the ncu "
-                            "capture summarised in profiles/adder_kernels_c16to16_32x32_b256.txt; algorithmic bytes of "
-                            "that launch: %d" % ALGO_BYTES_16x16.get(dom_kernel, 0),
+            "traffic": NCU_DRAM_BYTES.get(dom),
+            "traffic_note": "dram read+write bytes of ONE launch of this kernel on the 16->16 32x32 layer at batch 256, "
+                            f"ncu capture summarised in {NCU_CAPTURE}; algorithmic bytes of that launch: "
+                            f"{ALGO_BYTES_16x16.get(dom, 0)}",
+            "per_kernel": {KERNEL_NAMES[k]: {"ms_total": tot[k], "frac": 3 * tot_T / (tot[k] * 1e-3) / fp32_peak,
+                                             "traffic": NCU_DRAM_BYTES.get(k), "algorithmic_bytes": ALGO_BYTES_16x16.get(k)}
+                           for k in ("fwd", "grad_x", "grad_w")},
         }
         line["adder_conv"] = {
-            "workload": "the 20 adder layers of ResNet-20 at batch 256, kernels timed alone (L2 flushed)",
+            "workload": "the 20 adder layers of ResNet-20 at batch 256, every kernel timed alone, one launch per sample, L2 flushed before each",
             "fwd_ms": tot["fwd"], "grad_x_ms": tot["grad_x"], "grad_w_ms": tot["grad_w"],
             "fwd_bwd_gops": 9 * tot_T / (all_ms * 1e-3) / 1e9, "pct_fp32_peak": 100 * 9 * tot_T / (all_ms * 1e-3) / fp32_peak,
             "bwd_ms": tot["bwd"], "bwd_note": "both gradient kernels issued as the layer's backward does (weight gradient on a side stream)",
             "pass_gops": 9 * tot_T / (pass_ms * 1e-3) / 1e9, "pass_pct_fp32_peak": 100 * 9 * tot_T / (pass_ms * 1e-3) / fp32_peak,
             "share_of_step": pass_ms / (ms_total / K),
         }
+        # the per-layer sweep of the benchmark definition, with two columns beside it: the reference's own
+        # CUDA path (its adder.py + its kernels built for sm_100, from baseline/_ref) timed on this GPU with
+        # the same events, and its CPU path (the port of adder.py) on the host cores
+        ref_adder, ref_why = load_reference_cuda() if not args.skip_reference_cuda else (None, "skipped by flag")
+        cpu_cols = world == 1 and not args.skip_cpu_baseline
+        cores = os.cpu_count() or 1
         sweep = []
         for shp in SWEEP_SHAPES:
             t = time_layer_ops(256, shp)
@@ -393,11 +556,24 @@ def run_gpu_arm(args):
             ms = t["fwd"] + t["grad_x"] + t["grad_w"]
             ci, co, h, w, s, k, p = shp
             x_b, w_b, o_b = 256 * ci * h * w * 4, co * ci * k * k * 4, T // (ci * k * k) * 4
-            sweep.append({"shape": {"ci": ci, "co": co, "h": h, "w": w, "stride": s, "k": k}, "fwd_ms": t["fwd"],
-                          "grad_x_ms": t["grad_x"], "grad_w_ms": t["grad_w"], "bwd_ms": t["bwd"],
-                          "pass_pct_fp32_peak": 100 * 9 * T / ((t["fwd"] + t["bwd"]) * 1e-3) / fp32_peak,
-                          "fwd_bwd_gops": 9 * T / (ms * 1e-3) / 1e9, "pct_fp32_peak": 100 * 9 * T / (ms * 1e-3) / fp32_peak,
-                          "fwd_gbs": (x_b + w_b + o_b) / (t["fwd"] * 1e-3) / 1e9})
+            row = {"shape": {"ci": ci, "co": co, "h": h, "w": w, "stride": s, "k": k}, "fwd_ms": t["fwd"],
+                   "grad_x_ms": t["grad_x"], "grad_w_ms": t["grad_w"], "bwd_ms": t["bwd"],
+                   "pass_pct_fp32_peak": 100 * 9 * T / ((t["fwd"] + t["bwd"]) * 1e-3) / fp32_peak,
+                   "fwd_bwd_gops": 9 * T / (ms * 1e-3) / 1e9, "pct_fp32_peak": 100 * 9 * T / (ms * 1e-3) / fp32_peak,
+                   "fwd_gbs": (x_b + w_b + o_b) / (t["fwd"] * 1e-3) / 1e9}
+            if ref_adder is not None and reference_cuda_in_bounds(256, shp):
+                rf, rb = time_reference_cuda(ref_adder, 256, shp)
+                row["reference_cuda"] = {"fwd_ms": rf, "bwd_ms": rb, "fwd_bwd_gops": 9 * T / ((rf + rb) * 1e-3) / 1e9}
+                row["vs_reference_cuda"] = (rf + rb) / (t["fwd"] + t["bwd"])
+            if cpu_cols:
+                # CIFAR-size layers in full; the ImageNet-size ones (3e10 triples) on a batch-16 slice, scaled x16
+                nb = 256 if T < 2e9 else 16
+                sec = time_layer_cpu(nb, shp, iters=2 if nb == 256 else 1) * (256 / nb)
+                row["cpu"] = {"fwd_bwd_s": sec, "fwd_bwd_gops": 9 * T / sec / 1e9, "cores": cores, "batch_timed": nb}
+            sweep.append(row)
+        line["reference_cuda"] = {"available": ref_adder is not None, "why_not": ref_why,
+                                  "what": "the reference's adder2d_function forward + autograd backward (unfold, permutes, "
+                                          "CONV / CONV_BACKWARD built for sm_100, col2im, rescale), same CUDA events, batch 256"}
         line["layers"] = sweep
         # the two 1x1 stride-2 downsample layers (about 6 op/B): bound by memory traffic, reported as GB/s of
         # algorithmic bytes (each tensor once; only the sampled quarter of x) against the measured HBM peak
@@ -415,12 +591,24 @@ def run_gpu_arm(args):
         line["hbm"] = {"peak_gbs": hbm_peak, "note": "the 3x3 and the wide 1x1 adder layers are FP32-issue bound (54-1460 op/B against a "
                        "machine balance of ~11 op/B); the 1x1 stride-2 downsample layers are in hbm_layers"}
 
+    # ---- ResNet-50 (ImageNet shapes, batch 64 per GPU): a few steps of the other network the benchmark names
+    if rank == 0 and world == 1 and args.workload == "resnet20" and not args.skip_resnet50:
+        line["resnet50"] = resnet50_block(dev, fp32_peak if not args.skip_layers else None)
+
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
         ips, b, s_per_step = cpu_images_per_s(args.cpu_budget_s, 2, 1)
         cores = os.cpu_count() or 1
         line["cpu_baseline"] = {"value": ips, "unit": "images/s", "cores": cores, "kind": "port",
                                 "sample": f"2 training steps of ResNet-20 at batch {b} (of 256) through the CPU port of the "
                                           f"reference's adder.py unfold path, {cores} host threads, {s_per_step:.1f} s/step"}
+        # configuration 1 of the benchmark definition: one adder2d layer, N=32, 16->16, 32x32, fwd+bwd on the host
+        cfg1 = (16, 16, 32, 32, 1, 3, 1)
+        sec = time_layer_cpu(32, cfg1, iters=3)
+        t1 = time_layer_ops(32, cfg1)
+        line["config1_single_layer"] = {
+            "shape": "N=32 Ci=16 Co=16 32x32 k3 s1 p1", "cpu_fwd_bwd_s": sec, "cpu_gops": 9 * triples(32, cfg1) / sec / 1e9,
+            "cpu_cores": cores, "cpu_sample": "1 warm-up + 3 timed forward+backward passes, median",
+            "gpu_fwd_ms": t1["fwd"], "gpu_bwd_ms": t1["bwd"], "gpu_gops": 9 * triples(32, cfg1) / ((t1["fwd"] + t1["bwd"]) * 1e-3) / 1e9}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -442,13 +630,17 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=["resnet20", "resnet50"], default="resnet20")
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch (default 256 for resnet20, 64 for resnet50)")
-    ap.add_argument("--bucket-mb", type=float, default=25.0)
+    ap.add_argument("--bucket-mb", type=float, default=None,
+                    help="gradient bucket size; default: a third of the model's gradients, at most 25 MB")
     ap.add_argument("--sync-bn", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--exact-clamp", action="store_true", help="input gradient with min/max instead of the saturating add")
     ap.add_argument("--skip-layers", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
-    ap.add_argument("--cpu-budget-s", type=float, default=90.0)
+    ap.add_argument("--skip-resnet50", action="store_true")
+    ap.add_argument("--skip-reference-cuda", action="store_true")
+    ap.add_argument("--cpu-budget-s", type=float, default=150.0,
+                    help="time budget of the CPU arm: the sample batch is the largest (up to 256) that fits it")
     args = ap.parse_args()
     if args.batch is None:
         args.batch = 256 if args.workload == "resnet20" else 64

@@ -80,9 +80,4 @@ def draw_cols(case):
     return W, X, g
 
 
-def resnet20_batch(batch, seed):
-    """Synthetic CIFAR-shaped batch: images ~ N(0,1) [B,3,32,32], labels uniform over 10 classes."""
-    rng = np.random.default_rng(seed + 7)
-    images = rng.standard_normal((batch, 3, 32, 32)).astype(np.float32)
-    labels = rng.integers(0, 10, size=(batch,)).astype(np.int64)
-    return images, labels
+from addernetcuda_b200.synthetic import resnet20_batch  # noqa: E402,F401  (re-exported for the tests)

@@ -16,7 +16,7 @@ SHAPES = [(64, 16, 32, 32), (8, 5, 7, 7), (4, 64, 8, 8), (3, 3, 1, 1), (2, 7, 5,
 @pytest.mark.parametrize("mode", ["plain", "relu", "residual_relu"])
 def test_fused_batchnorm_matches_torch(shape, mode):
     from addernetcuda_b200.batchnorm import FusedBatchNorm2d
-    torch.manual_seed(hash((shape, mode)) % 1000)
+    torch.manual_seed(sum(shape) * 3 + ["plain", "relu", "residual_relu"].index(mode))
     n, c, h, w = shape
     y = torch.randn(shape) * 3 + 1.5
     res = torch.randn(shape) if mode == "residual_relu" else None
@@ -26,6 +26,14 @@ def test_fused_batchnorm_matches_torch(shape, mode):
     with torch.no_grad():
         ref.weight.copy_(torch.rand(c) + 0.5)
         ref.bias.copy_(torch.randn(c) * 0.3)
+    if relu:
+        # Whether a pre-activation within rounding of zero passes the ReLU is a coin toss between fp32 and
+        # fp64; no gradient is sent through those (few) elements, so that the mask does not enter the comparison.
+        with torch.no_grad():
+            probe = nn.BatchNorm2d(c).double()
+            probe.load_state_dict(ref.state_dict())
+            pre = probe.train()(y.double()) + (res.double() if res is not None else 0.0)
+            dz[pre.abs() < 1e-4] = 0.0
     bn = FusedBatchNorm2d(c).to(DEV)
     bn.load_state_dict({k: v.float() for k, v in ref.state_dict().items()})
     ref.train(); bn.train()

@@ -4,7 +4,8 @@ that do not need a full-size CPU result:
     full batch must match the oracle run on just those images;
   * the unscaled weight gradient is additive over the batch: halves sum to the whole;
   * the rescaled weight gradient has L2 norm eta * sqrt(numel) (adder.py:78);
-  * the result for a sub-batch is bitwise the same whether computed alone or inside the big batch.
+  * a sub-batch computed alone agrees with the same images inside the big batch, and the same call twice
+    gives the same bits.
 """
 import math
 
@@ -74,7 +75,16 @@ def test_full_batch_properties(shape):
     print("   ", msg)
     assert ok, msg
 
-    # (4) sub-batch alone == sub-batch inside the big batch, bit for bit
+    # (4) a sub-batch computed alone agrees with the same images inside the big batch.  (Not bit for bit:
+    # how many thread groups share a reduction depends on the parallelism the whole batch offers, so the
+    # order of summation can differ between batch sizes; it is fixed for a given geometry.)
     sub = slice(64, 72)
-    assert torch.equal(ac.forward(x[sub].contiguous(), wt, s, p), out[sub])
-    assert torch.equal(ac.backward_input(g[sub].contiguous(), x[sub].contiguous(), wt, s, p), gx[sub])
+    for name, got, want in (("sub-batch out", ac.forward(x[sub].contiguous(), wt, s, p), out[sub]),
+                            ("sub-batch grad_x", ac.backward_input(g[sub].contiguous(), x[sub].contiguous(), wt, s, p), gx[sub])):
+        ok, worst, msg = O.compare(name, got, want)
+        print("   ", msg)
+        assert ok, msg
+    # (5) and the same call twice gives the same bits
+    assert torch.equal(ac.forward(x, wt, s, p), out)
+    assert torch.equal(ac.backward_input(g, x, wt, s, p), gx)
+    assert torch.equal(ac.backward_weight(g, x, wt, s, p), gw)

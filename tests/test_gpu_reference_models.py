@@ -50,10 +50,8 @@ def _reference_model(module_name, ctor):
 
 
 def _network_batch(z):
-    rng = np.random.default_rng(int(z["seed"]) + 7)
-    b, hw, classes = int(z["batch"]), int(z["in_hw"]), int(z["classes"])
-    images = rng.standard_normal((b, 3, hw, hw)).astype(np.float32)
-    labels = rng.integers(0, classes, size=(b,)).astype(np.int64)
+    from addernetcuda_b200.synthetic import image_batch
+    images, labels = image_batch(int(z["batch"]), int(z["in_hw"]), int(z["classes"]), int(z["seed"]))
     return torch.from_numpy(images).to(DEV), torch.from_numpy(labels).to(DEV)
 
 
