@@ -47,6 +47,7 @@ SIGNATURES = {
                                              c_int, c_int, c_int, c_void_p]),
     "adder_b200_batchnorm_backward": (c_int, [c_void_p] * 10 + [c_int, c_void_p, c_size_t, c_int, c_int, c_int,
                                               c_void_p]),
+    "adder_b200_affine_forward": (c_int, [c_void_p] * 5 + [c_int, c_int, c_int, c_int, c_void_p]),
     "adder_b200_describe_plan": (c_int, [c_int, *_GEOM, c_int, c_char_p, c_size_t]),
 }
 # exported by libadder_b200_tuning.so only (the header's ADDER_B200_TUNING section)

@@ -265,11 +265,60 @@ static int bn_geom(int n, int c, int hw, BnGeom* g) {
     return ADDER_OK;
 }
 
+// Evaluation mode: batch norm with running statistics is a fixed per-channel affine map, so the layer after
+// an adder convolution collapses to z = y*scale[c] + shift[c] [+ residual] [ReLU] in one pass.
+__global__ void __launch_bounds__(BN_THREADS) affine_act_kernel(const float* __restrict__ y, const float* __restrict__ scale,
+                                                                const float* __restrict__ shift,
+                                                                const float* __restrict__ residual, float* __restrict__ z,
+                                                                int relu, int C, int HW, long long total, int vec) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    if (vec) {
+        const int hw4 = HW >> 2;
+        for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < (total >> 2); q += stride) {
+            const int c = (int)((q / hw4) % C);
+            const float sc = __ldg(scale + c), sh = __ldg(shift + c);
+            float4 v = reinterpret_cast<const float4*>(y)[q];
+            v.x = fmaf(v.x, sc, sh); v.y = fmaf(v.y, sc, sh); v.z = fmaf(v.z, sc, sh); v.w = fmaf(v.w, sc, sh);
+            if (residual != nullptr) {
+                const float4 r = reinterpret_cast<const float4*>(residual)[q];
+                v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
+            }
+            if (relu) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); }
+            reinterpret_cast<float4*>(z)[q] = v;
+        }
+    } else {
+        for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+            const int c = (int)((e / HW) % C);
+            float v = fmaf(y[e], __ldg(scale + c), __ldg(shift + c));
+            if (residual != nullptr) v += residual[e];
+            z[e] = relu ? fmaxf(v, 0.f) : v;
+        }
+    }
+}
+
 }  // namespace adder
 
 using namespace adder;
 
 extern "C" {
+
+int adder_b200_affine_forward(const float* y, const float* scale, const float* shift, const float* residual, float* z,
+                              int relu, int n, int c, int hw, void* stream) {
+    if (n < 0 || c <= 0 || hw <= 0) return ADDER_ERR_BAD_SHAPE;
+    if (n == 0) return ADDER_OK;
+    if (y == nullptr || scale == nullptr || shift == nullptr || z == nullptr) return ADDER_ERR_NULL_POINTER;
+    const long long total = (long long)n * c * hw;
+    uintptr_t bits = reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(z);
+    if (residual != nullptr) bits |= reinterpret_cast<uintptr_t>(residual);
+    const int vec = (hw % 4 == 0 && (bits & 15) == 0) ? 1 : 0;
+    const long long work = vec ? total / 4 : total;
+    long long blocks = (work + BN_THREADS - 1) / BN_THREADS;
+    const long long cap = 8LL * sm_count();
+    if (blocks > cap) blocks = cap;
+    affine_act_kernel<<<(unsigned)blocks, BN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(y, scale, shift, residual, z,
+                                                                                             relu, c, hw, total, vec);
+    return launched();
+}
 
 size_t adder_b200_batchnorm_workspace_bytes(int n, int c, int hw) {
     BnGeom g;

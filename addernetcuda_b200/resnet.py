@@ -30,8 +30,9 @@ def _norm_class(fused: bool):
 
 
 def _bn_act(bn, y, residual=None, relu=False):
-    """relu?(bn(y) + residual?) - one fused pass when `bn` is a FusedBatchNorm2d."""
-    if hasattr(bn, "forward") and bn.__class__.__name__ == "FusedBatchNorm2d":
+    """relu?(bn(y) + residual?) - one fused pass when `bn` is a FusedBatchNorm2d (training) or a
+    FoldedBatchNorm2d (evaluation, `inference.fold_batchnorm`)."""
+    if bn.__class__.__name__ in ("FusedBatchNorm2d", "FoldedBatchNorm2d"):
         return bn(y, residual=residual, relu=relu)
     out = bn(y)
     if residual is not None:

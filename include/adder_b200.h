@@ -170,6 +170,13 @@ ADDER_API int adder_b200_batchnorm_backward(const float* dz, const float* y, con
                                             float* dresidual, float* dgamma, float* dbeta, int relu, void* workspace,
                                             size_t workspace_bytes, int n, int c, int hw, void* stream);
 
+/* Evaluation mode of the same layer: with running statistics batch norm is the per-channel affine map
+ * scale = gamma / sqrt(running_var + eps), shift = beta - running_mean * scale, so the layer after an adder
+ * convolution is z = y*scale[c] + shift[c] [+ residual] [then ReLU] in one pass over [n, c, hw] (what
+ * test.py:68-90 of the reference evaluates through nn.BatchNorm2d.eval()).  residual may be NULL. */
+ADDER_API int adder_b200_affine_forward(const float* y, const float* scale, const float* shift, const float* residual,
+                                        float* z, int relu, int n, int c, int hw, void* stream);
+
 #ifdef ADDER_B200_TUNING
 /* ---- tuning build only (libadder_b200_tuning.so, compiled with -DADDER_B200_TUNING) ---------------
  * The product library exports none of these and keeps no tile state: any thread calling a setter would

@@ -156,3 +156,46 @@ def test_reference_checkpoint_keys_load():
     stripped = {k[len("module."):]: v for k, v in sd.items()}
     missing, unexpected = R.resnet20().load_state_dict(stripped, strict=True)
     assert not missing and not unexpected
+
+
+def test_folded_batchnorm_inference_and_topk_harness():
+    """The inference path: a checkpoint with the reference's `module.` key prefix loads, batch norm folds into
+    a one-kernel per-channel affine epilogue (with the residual add and ReLU), the folded network's logits
+    equal the unfolded evaluation-mode ones and the CPU oracle network's, and the top-1 / top-5 harness
+    counts like a plain NumPy evaluation of the same logits."""
+    from addernetcuda_b200 import inference as I, resnet as R
+    from oracle import adder_unfold as U
+    net = _build()
+    images, labels = resnet20_batch(32, SEED)
+    xg, yg = torch.from_numpy(images).to(DEV), torch.from_numpy(labels).to(DEV)
+    net.train()
+    with torch.no_grad():
+        net(xg); net(xg * 0.7 - 0.2)                 # non-trivial running statistics
+    checkpoint = {"module." + k: v.detach().cpu().clone() for k, v in net.state_dict().items()}
+    fresh = R.resnet20().to(DEV)
+    missing, unexpected = I.load_reference_checkpoint(fresh, checkpoint)
+    assert not missing and not unexpected
+    fresh.eval()
+    with torch.no_grad():
+        plain = fresh(xg)
+    folded = I.fold_batchnorm(fresh)
+    assert not any(isinstance(m, torch.nn.BatchNorm2d) for m in folded.modules())
+    with torch.no_grad():
+        got = folded(xg)
+    ok, err, msg = O.compare("folded vs unfolded eval logits", got, plain, abs_=2e-4)
+    print("   ", msg)
+    assert ok, msg
+    ref = R.resnet20(conv=U.adder2d)
+    I.load_reference_checkpoint(ref, checkpoint)
+    ref.eval()
+    with torch.no_grad():
+        want = ref(torch.from_numpy(images))
+    ok, err, msg = O.compare("folded eval logits vs oracle network", got, want, abs_=2e-4)
+    print("   ", msg)
+    assert ok, msg
+    # top-k harness against NumPy on the oracle's logits
+    top1, top5 = I.validate([(xg[:16], yg[:16]), (xg[16:], yg[16:])], folded, topk=(1, 5))
+    order = np.argsort(-want.numpy(), axis=1)
+    want1 = 100.0 * np.mean(order[:, 0] == labels)
+    want5 = 100.0 * np.mean([labels[i] in order[i, :5] for i in range(len(labels))])
+    assert abs(top1 - want1) < 1e-3 and abs(top5 - want5) < 1e-3, (top1, want1, top5, want5)
