@@ -48,6 +48,7 @@ SIGNATURES = {
     "adder_b200_batchnorm_backward": (c_int, [c_void_p] * 10 + [c_int, c_void_p, c_size_t, c_int, c_int, c_int,
                                               c_void_p]),
     "adder_b200_affine_forward": (c_int, [c_void_p] * 5 + [c_int, c_int, c_int, c_int, c_void_p]),
+    "adder_b200_device_status": (c_int, [POINTER(c_int), c_int]),
     "adder_b200_describe_plan": (c_int, [c_int, *_GEOM, c_int, c_char_p, c_size_t]),
 }
 # exported by libadder_b200_tuning.so only (the header's ADDER_B200_TUNING section)
@@ -122,3 +123,10 @@ def describe_plan(op: int, n, ci, h, w, co, k, stride, pad, flags: int = 0) -> s
     buf = ctypes.create_string_buffer(512)
     check(load().adder_b200_describe_plan(op, n, ci, h, w, co, k, stride, pad, flags, buf, 512), "describe_plan")
     return buf.value.decode()
+
+
+def device_status(reset: bool = True) -> int:
+    """0 unless a kernel's bounded wait for the copy engine ran out on the current device."""
+    v = c_int(0)
+    check(load().adder_b200_device_status(ctypes.byref(v), int(reset)), "adder_b200_device_status")
+    return v.value

@@ -115,13 +115,16 @@ __device__ __forceinline__ void gx_scale_weights(const GxArgs& a, float* wt, int
     }
 }
 
-template <int KS, int S, int RW, int RC, bool FAST>
-__global__ void __launch_bounds__(256, 2) adder_gx_kernel(const GxArgs a) {
+// MB = CTAs per SM the register budget is cut for.  A layer whose output channels fit one chunk needs one
+// stage of shared memory only, and with 4-pixel segments few enough registers for three CTAs per SM: the
+// third CTA's loads and stores then run under the other two's arithmetic (16->16 32x32: 69 -> 66 us).
+template <int KS, int S, int RW, int RC, bool FAST, int MB = 2>
+__global__ void __launch_bounds__(256, MB) adder_gx_kernel(const GxArgs a) {
     constexpr int KK = KS * KS;
     extern __shared__ __align__(16) float smem[];
     float* const Gs = smem;
-    float* const Wt = smem + 2 * a.gs_stage;
-    float* const G1 = Wt + 2 * a.ws_stage;
+    float* const Wt = smem + a.nstages * a.gs_stage;
+    float* const G1 = Wt + a.nstages * a.ws_stage;
     float* const Tot = G1 + a.g1_size + threadIdx.x;   // [RC*RW][blockDim.x] running totals, one column per thread
 
     const int tid = threadIdx.x;
@@ -412,8 +415,8 @@ __global__ void __launch_bounds__(256, 2) adder_gx_s2pair_kernel(const GxArgs a)
     constexpr int S = 2, KK = KS * KS, NSEG = 2;
     extern __shared__ __align__(16) float smem[];
     float* const Gs = smem;
-    float* const Wt = smem + 2 * a.gs_stage;
-    float* const G1 = Wt + 2 * a.ws_stage;
+    float* const Wt = smem + a.nstages * a.gs_stage;
+    float* const G1 = Wt + a.nstages * a.ws_stage;
     float* const Tot = G1 + a.g1_size + threadIdx.x;   // [NSEG*RC*RW][blockDim.x]
 
     const int tid = threadIdx.x;
@@ -705,7 +708,11 @@ static int plan_gx_n(const Geom& g, const TileHint& hint, GxPlan& p, int nseg) {
     pd.CH = cko;
     a.gs_stage = round_up(cko * a.CH_STRIDE, 4);
     a.ws_stage = cko * KS * KS * a.TCIP;
-    const size_t smem = ((size_t)2 * (a.gs_stage + a.ws_stage) + a.g1_size + (size_t)RC * RW * threads * nseg) * sizeof(float);
+    const int nchunks = ceil_div(g.Co, cko);
+    a.nstages = nchunks > 1 ? 2 : 1;
+    // running totals in shared memory only where the kernels use them (several chunks, or the 1x1 kernels)
+    const size_t tot = (nseg == 2 || KS == 1 || nchunks > 1) ? (size_t)RC * RW * threads * nseg : 0;
+    const size_t smem = ((size_t)a.nstages * (a.gs_stage + a.ws_stage) + a.g1_size + tot) * sizeof(float);
     p.smem = smem;
     if (smem > 200 * 1024) return ADDER_ERR_UNSUPPORTED;
     pd.d_cols = FastDiv(pd.COLS);
@@ -757,6 +764,14 @@ static int launch_gx_t(const Geom& g, const float* gout, const float* x, const f
             return launched();
         }
     }
+    if constexpr (S == 1 && RW == 4 && KS == 3) {
+        if (p.a.nstages == 1 && 3 * (p.smem + 1024) <= 227 * 1024) {
+            auto kern3 = adder_gx_kernel<KS, S, RW, RC, FAST, 3>;
+            if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern3), p.smem) != ADDER_OK) return ADDER_ERR_CUDA;
+            kern3<<<dim3((unsigned)p.gx, (unsigned)p.gy), p.threads, p.smem, stream>>>(p.a);
+            return launched();
+        }
+    }
     auto kern = adder_gx_kernel<KS, S, RW, RC, FAST>;
     if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), p.smem) != ADDER_OK) return ADDER_ERR_CUDA;
     kern<<<dim3((unsigned)p.gx, (unsigned)p.gy), p.threads, p.smem, stream>>>(p.a);
@@ -789,7 +804,6 @@ int describe_gx(const Geom& g, int fast, const TileHint& hint, char* buf, size_t
                  "grid=(%d,%d) status=0", g.stride, fast, ceil_div(g.N * g.Ho * g.Wo, 256), ceil_div(g.Ci, 16));
         return ADDER_OK;
     }
-    if (gx_pipe_applicable(g, hint)) return describe_gx_pipe(g, fast, hint, buf, n);
     const int rw = choose_gx_rw(g, hint);
     GxPlan p;
     int st = ADDER_ERR_UNSUPPORTED;
@@ -808,7 +822,6 @@ int describe_gx(const Geom& g, int fast, const TileHint& hint, char* buf, size_t
 int launch_gx(const Geom& g, const float* gout, const float* x, const float* w, float* gx, int fast,
               int accumulate, const TileHint& hint, cudaStream_t stream) {
     if (hint.is_default() && pointwise_applicable(g)) return launch_pointwise_gx(g, gout, x, w, gx, fast, accumulate, stream);
-    if (gx_pipe_applicable(g, hint)) return launch_gx_pipe(g, gout, x, w, gx, fast, accumulate, hint, stream);
     const int rw = choose_gx_rw(g, hint);
 #define ADDER_GX_LAUNCH(KS_, S_, RW_, RC_, FAST_) \
     return launch_gx_t<KS_, S_, RW_, RC_, FAST_>(g, gout, x, w, gx, accumulate, hint, stream);

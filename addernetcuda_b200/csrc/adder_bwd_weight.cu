@@ -330,6 +330,7 @@ struct GwPlan {
     bool use_1x1 = false;   // 1x1 stride-1 layers with enough channels take the GEMM-style kernel
     bool use_pointwise = false;   // 1x1 stride-2 layers with few channels: adder_pointwise.cu
     bool use_pipe = false;        // 3x3 layers with channels in sixteens: adder_bwd_weight_pipe.cu
+    bool use_tma = false;         // ... and stride 1, rows of 8-pixel segments: adder_bwd_weight_tma.cu
 };
 
 template <int KS, int S, int RW, int RM, int RC>
@@ -456,6 +457,14 @@ static GwPlan plan_gw(const Geom& g, const TileHint& hint) {
             p.a.splits = sp;
         }
     }
+    if (p.status == ADDER_OK && gw_tma_applicable(g, hint)) {
+        const int sp = gw_tma_splits(g, hint);
+        if (sp > 0) {
+            p.use_tma = true;
+            p.use_pipe = false;
+            p.a.splits = sp;
+        }
+    }
     if (p.status == ADDER_OK && gw1x1_applicable(g) && hint.rm != 9) {
         p.use_1x1 = true;
         p.a.splits = gw1x1_splits(g);
@@ -482,6 +491,7 @@ static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 int describe_gw(const Geom& g, const TileHint& hint, char* buf, size_t n) {
     const GwPlan p = plan_gw(g, hint);
+    if (p.status == ADDER_OK && p.use_tma) return describe_gw_tma(g, hint, buf, n);
     if (p.status == ADDER_OK && p.use_pipe) return describe_gw_pipe(g, hint, buf, n);
     if (p.status == ADDER_ERR_UNSUPPORTED && !((g.k == 1 || g.k == 3) && (g.stride == 1 || g.stride == 2))) return p.status;
     const GwArgs& a = p.a;
@@ -532,7 +542,16 @@ int launch_gw(const Geom& g, const float* gout, const float* x, const float* w, 
 
     const bool rw7 = (g.Wo % 8 != 0) && (g.Wo % 7 == 0);
     int st = ADDER_ERR_UNSUPPORTED;
-    if (p.use_pipe) st = launch_gw_pipe(g, gout, x, p.a.part, p.a.gsum_part, ticket, p.a.splits, hint, stream);
+    if (p.use_tma) {
+        st = launch_gw_tma(g, gout, x, p.a.part, p.a.gsum_part, ticket, p.a.splits, hint, stream);
+        if (st == ADDER_ERR_ALIGNMENT) {
+            // no tensor map for these pointers (not 16-byte aligned): the cp.async kernel, same number of slices
+            TileHint h2 = hint;
+            h2.ti = p.a.splits;
+            st = launch_gw_pipe(g, gout, x, p.a.part, p.a.gsum_part, ticket, p.a.splits, h2, stream);
+        }
+    }
+    else if (p.use_pipe) st = launch_gw_pipe(g, gout, x, p.a.part, p.a.gsum_part, ticket, p.a.splits, hint, stream);
     else if (p.use_pointwise) st = launch_pointwise_gw(g, gout, x, p.a.part, p.a.gsum_part, ticket, p.a.splits, stream);
     else if (p.use_1x1) st = launch_gw1x1(g, gout, x, p.a.part, p.a.gsum_part, ticket, p.a.splits, stream);
     else if (g.k == 3 && g.stride == 1) st = rw7 ? launch_main_t<3, 1, 7, 4, 2>(p, stream) : launch_main_t<3, 1, 8, 4, 2>(p, stream);

@@ -334,7 +334,6 @@ int describe_fwd(const Geom& g, const TileHint& hint, char* buf, size_t n) {
                  "grid=(%d,%d) status=0", g.stride, ceil_div(g.N * g.Ho * g.Wo, 256), ceil_div(g.Co, 16));
         return ADDER_OK;
     }
-    if (fwd_pipe_applicable(g, hint)) return describe_fwd_pipe(g, hint, buf, n);
     int rw = 8, rm = 8;
     choose_fwd_tile(g, hint, rw, rm);
     FwdPlan p;
@@ -354,7 +353,6 @@ int describe_fwd(const Geom& g, const TileHint& hint, char* buf, size_t n) {
 int launch_fwd(const Geom& g, const float* x, const float* w, float* out, const TileHint& hint,
                cudaStream_t stream) {
     if (hint.is_default() && pointwise_applicable(g)) return launch_pointwise_fwd(g, x, w, out, stream);
-    if (fwd_pipe_applicable(g, hint)) return launch_fwd_pipe(g, x, w, out, hint, stream);
     int rw = 8, rm = 8;
     choose_fwd_tile(g, hint, rw, rm);
 #define ADDER_FWD_LAUNCH(KS_, S_, RW_, RM_) return launch_fwd_t<KS_, S_, RW_, RM_>(g, x, w, out, hint, stream);

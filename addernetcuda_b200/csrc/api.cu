@@ -76,11 +76,18 @@ int ensure_dynamic_smem(const void* kernel, size_t bytes) {
         int optin = 0;
         if (cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess || optin <= 0)
             return ADDER_ERR_CUDA;
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, optin) != cudaSuccess) {
+        // the opt-in limit covers static and dynamic shared memory together
+        cudaFuncAttributes fa;
+        if (cudaFuncGetAttributes(&fa, kernel) != cudaSuccess) {
             (void)cudaGetLastError();
             return ADDER_ERR_CUDA;
         }
-        it = granted.emplace(std::make_pair(kernel, dev), (size_t)optin).first;
+        const int dyn = optin - (int)fa.sharedSizeBytes;
+        if (dyn <= 0 || cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return ADDER_ERR_CUDA;
+        }
+        it = granted.emplace(std::make_pair(kernel, dev), (size_t)dyn).first;
     }
     return bytes <= it->second ? ADDER_OK : ADDER_ERR_UNSUPPORTED;
 }
@@ -233,7 +240,7 @@ int adder_b200_set_tile_hint(int op, int threads, int channel_groups, int tile_r
 }
 
 int adder_b200_set_variant(int op, int variant) {
-    if (op < 0 || op > 2 || variant < 0 || variant > 1) return ADDER_ERR_BAD_SHAPE;
+    if (op < 0 || op > 2 || variant < 0 || variant > 2) return ADDER_ERR_BAD_SHAPE;
     g_hints[op].variant.store(variant);
     return ADDER_OK;
 }

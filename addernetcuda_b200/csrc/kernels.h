@@ -18,7 +18,8 @@ struct TileHint {
     int smem_kb = 0;   // shared-memory budget per CTA
     int rw = 0;        // pixels per thread segment (register tile width)
     int rm = 0;        // channels per thread (register tile height)
-    int variant = 0;   // 0 = choose the kernel family automatically, 1 = the non-persistent kernels
+    int variant = 0;   // weight gradient: 0 = automatic, 1 = the tiled kernel with pixel lanes, 2 = the warp-tile
+                       // kernel that stages with cp.async where the default would use tiled bulk copies
     bool is_default() const { return !(threads | cg | th | ti | ck | smem_kb | rw | rm | variant); }
 };
 
@@ -47,6 +48,7 @@ struct GxArgs {
     int vec_io;          // x is read and grad_x written as aligned quads
     int nseg;            // segments per thread: 2 in the paired stride-2 kernel, else 1
     int WPP, wgroups;    // weight staging: pairs per pass and output-channel groups (adder_bwd_input.cu)
+    int nstages;         // shared-memory stages: 2 when the output channels take several chunks, else 1
 };
 
 struct GwArgs {
@@ -93,17 +95,8 @@ inline int launched(int n = 1) {
 int ensure_dynamic_smem(const void* kernel, size_t bytes);
 
 int launch_fwd(const Geom& g, const float* x, const float* w, float* out, const TileHint& hint, cudaStream_t s);
-// Persistent multi-stage forward (adder_fwd_pipe.cu)
-bool fwd_pipe_applicable(const Geom& g, const TileHint& hint);
-int launch_fwd_pipe(const Geom& g, const float* x, const float* w, float* out, const TileHint& hint, cudaStream_t s);
-int describe_fwd_pipe(const Geom& g, const TileHint& hint, char* buf, size_t n);
 int launch_gx(const Geom& g, const float* gout, const float* x, const float* w, float* gx, int fast,
               int accumulate, const TileHint& hint, cudaStream_t s);
-// Persistent multi-stage input gradient of stride-1 layers (adder_bwd_input_pipe.cu)
-bool gx_pipe_applicable(const Geom& g, const TileHint& hint);
-int launch_gx_pipe(const Geom& g, const float* gout, const float* x, const float* w, float* gx, int fast,
-                   int accumulate, const TileHint& hint, cudaStream_t s);
-int describe_gx_pipe(const Geom& g, int fast, const TileHint& hint, char* buf, size_t n);
 size_t gw_workspace_bytes(const Geom& g, const TileHint& hint);
 int launch_gw(const Geom& g, const float* gout, const float* x, const float* w, float* gw, float eta,
               float* out_norm, int accumulate, void* workspace, size_t workspace_bytes, const TileHint& hint,
@@ -125,6 +118,13 @@ int gw_pipe_splits(const Geom& g, const TileHint& hint);
 int launch_gw_pipe(const Geom& g, const float* gout, const float* x, float* part, float* gsum_part,
                    unsigned int* ticket, int splits, const TileHint& hint, cudaStream_t stream);
 int describe_gw_pipe(const Geom& g, const TileHint& hint, char* buf, size_t n);
+
+// The same fed by tiled bulk copies (adder_bwd_weight_tma.cu): 3x3 stride-1 layers
+bool gw_tma_applicable(const Geom& g, const TileHint& hint);
+int gw_tma_splits(const Geom& g, const TileHint& hint);
+int launch_gw_tma(const Geom& g, const float* gout, const float* x, float* part, float* gsum_part,
+                  unsigned int* ticket, int splits, const TileHint& hint, cudaStream_t stream);
+int describe_gw_tma(const Geom& g, const TileHint& hint, char* buf, size_t n);
 
 bool gw1x1_applicable(const Geom& g);
 int gw1x1_splits(const Geom& g);

@@ -177,6 +177,12 @@ ADDER_API int adder_b200_batchnorm_backward(const float* dz, const float* y, con
 ADDER_API int adder_b200_affine_forward(const float* y, const float* scale, const float* shift, const float* residual,
                                         float* z, int relu, int n, int c, int hw, void* stream);
 
+/* Kernels that wait for the copy engine do so with a bounded number of polls; a wait that runs out sets a
+ * flag on the device and the kernel returns early (its output is then garbage).  This reads the flag of the
+ * current device into *status (0 = never happened) and, with reset != 0, clears it.  Synchronises with
+ * the device.  No reference counterpart. */
+ADDER_API int adder_b200_device_status(int* status, int reset);
+
 #ifdef ADDER_B200_TUNING
 /* ---- tuning build only (libadder_b200_tuning.so, compiled with -DADDER_B200_TUNING) ---------------
  * The product library exports none of these and keeps no tile state: any thread calling a setter would
@@ -192,8 +198,9 @@ ADDER_API int adder_b200_set_tile_hint(int op, int threads, int channel_groups, 
  * channels per thread: 4 or 8; 0,0 restores the automatic choice). */
 ADDER_API int adder_b200_set_micro_tile(int op, int pixels_per_thread, int channels_per_thread);
 
-/* Kernel family of one op: 0 = automatic (persistent multi-stage kernels where they apply),
- * 1 = the non-persistent kernels everywhere. */
+/* Kernel family of the weight gradient (op 2; ignored for the other ops): 0 = automatic, 1 = the tiled
+ * kernel with pixel lanes everywhere, 2 = the warp-tile kernel that stages with cp.async where the default
+ * would use tiled bulk copies. */
 ADDER_API int adder_b200_set_variant(int op, int variant);
 #endif /* ADDER_B200_TUNING */
 

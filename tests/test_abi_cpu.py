@@ -41,9 +41,11 @@ def test_library_exports_every_declared_symbol():
         for n in names + tuning_names:
             assert hasattr(tlib, n), n
         assert tlib.adder_b200_set_tile_hint(7, 0, 0, 0, 0, 0, 0) == 2
-        assert tlib.adder_b200_set_variant(0, 1) == 0
-        assert "persistent" not in _lib.describe_plan(0, 256, 16, 32, 32, 16, 3, 1, 1, 0)
-    assert "persistent" in _lib.describe_plan(0, 256, 16, 32, 32, 16, 3, 1, 1, 0)     # overrides cleared on exit
+        assert tlib.adder_b200_set_variant(2, 1) == 0
+        assert "warp-tile" not in _lib.describe_plan(2, 256, 16, 32, 32, 16, 3, 1, 1, 0)
+        assert tlib.adder_b200_set_variant(2, 2) == 0
+        assert "warp-tile k=3" in _lib.describe_plan(2, 256, 16, 32, 32, 16, 3, 1, 1, 0)      # the cp.async form
+    assert "warp-tile tma" in _lib.describe_plan(2, 256, 16, 32, 32, 16, 3, 1, 1, 0)          # overrides cleared on exit
 
 
 def test_version_and_status_strings():

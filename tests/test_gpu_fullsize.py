@@ -4,8 +4,8 @@ that do not need a full-size CPU result:
     full batch must match the oracle run on just those images;
   * the unscaled weight gradient is additive over the batch: halves sum to the whole;
   * the rescaled weight gradient has L2 norm eta * sqrt(numel) (adder.py:78);
-  * a sub-batch computed alone agrees with the same images inside the big batch, and the same call twice
-    gives the same bits.
+  * the result for a sub-batch is bitwise the same whether computed alone or inside the big batch, and the
+    same call twice gives the same bits.
 """
 import math
 
@@ -75,15 +75,11 @@ def test_full_batch_properties(shape):
     print("   ", msg)
     assert ok, msg
 
-    # (4) a sub-batch computed alone agrees with the same images inside the big batch.  (Not bit for bit:
-    # how many thread groups share a reduction depends on the parallelism the whole batch offers, so the
-    # order of summation can differ between batch sizes; it is fixed for a given geometry.)
+    # (4) sub-batch alone == sub-batch inside the big batch, bit for bit (forward and input gradient are
+    # per-image sums whose chunking does not depend on the batch size)
     sub = slice(64, 72)
-    for name, got, want in (("sub-batch out", ac.forward(x[sub].contiguous(), wt, s, p), out[sub]),
-                            ("sub-batch grad_x", ac.backward_input(g[sub].contiguous(), x[sub].contiguous(), wt, s, p), gx[sub])):
-        ok, worst, msg = O.compare(name, got, want)
-        print("   ", msg)
-        assert ok, msg
+    assert torch.equal(ac.forward(x[sub].contiguous(), wt, s, p), out[sub])
+    assert torch.equal(ac.backward_input(g[sub].contiguous(), x[sub].contiguous(), wt, s, p), gx[sub])
     # (5) and the same call twice gives the same bits
     assert torch.equal(ac.forward(x, wt, s, p), out)
     assert torch.equal(ac.backward_input(g, x, wt, s, p), gx)

@@ -115,36 +115,36 @@ def test_every_register_tile(name, tile, golden, ac):
     x, w, g = (_gpu(a) for a in draw_layer(case))
     s, p = case["stride"], case["pad"]
     with _lib.tuning() as lib:
-        for variant in (0, 1):          # the persistent kernels where they apply, then the non-persistent ones
-            for op in range(3):
-                assert lib.adder_b200_set_variant(op, variant) == 0
-            assert lib.adder_b200_set_micro_tile(0, tile[0], tile[1]) == 0
-            assert lib.adder_b200_set_micro_tile(1, tile[0], 4) == 0
-            _assert(golden.check(name, "out", ac.forward(x, w, s, p)))
-            _assert(golden.check(name, "grad_x", ac.backward_input(g, x, w, s, p)))
-            _assert(golden.check(name, "grad_x", ac.backward_input(g, x, w, s, p, fast_clamp=True)))
+        assert lib.adder_b200_set_micro_tile(0, tile[0], tile[1]) == 0
+        assert lib.adder_b200_set_micro_tile(1, tile[0], 4) == 0
+        _assert(golden.check(name, "out", ac.forward(x, w, s, p)))
+        _assert(golden.check(name, "grad_x", ac.backward_input(g, x, w, s, p)))
+        _assert(golden.check(name, "grad_x", ac.backward_input(g, x, w, s, p, fast_clamp=True)))
 
 
-@pytest.mark.parametrize("case", [c for c in LAYER_CASES if c["name"].startswith(("cfg1", "r20", "r50_n1_c64to64", "r50_n2_c64to256"))],
+@pytest.mark.parametrize("variant", [1, 2], ids=["pixel-lane kernel", "warp-tile kernel with cp.async"])
+@pytest.mark.parametrize("case", [c for c in LAYER_CASES if c["k"] == 3 and c["ci"] % 16 == 0 and c["co"] % 16 == 0],
                          ids=lambda c: c["name"])
-def test_non_persistent_kernels_match_reference_outputs(case, golden, ac):
-    """The layers that take the persistent kernels by default, through the non-persistent ones (which
-    remain the path of every geometry the persistent kernels do not cover)."""
+def test_weight_gradient_kernel_families(case, variant, golden, ac):
+    """3x3 layers with channels in sixteens take the warp-tile weight-gradient kernel fed by tiled bulk copies
+    (stride 1) or by cp.async (stride 2, unaligned tensors).  The other two families, which remain the path
+    of every geometry the default does not cover, must give the reference's gradient on the same layers."""
     from addernetcuda_b200 import _lib
     x, w, g = (_gpu(a) for a in draw_layer(case))
     s, p = case["stride"], case["pad"]
+    shape = (case["n"], case["ci"], case["h"], case["w"], case["co"], case["k"], s, p)
+    default_plan = _lib.describe_plan(2, *shape, 0)
     with _lib.tuning() as lib:
-        for op in range(3):
-            assert lib.adder_b200_set_variant(op, 1) == 0
-        for op in range(3):
-            assert "persistent" not in _lib.describe_plan(op, case["n"], case["ci"], case["h"], case["w"], case["co"],
-                                                          case["k"], s, p, 1)
-            assert "warp-tile" not in _lib.describe_plan(op, case["n"], case["ci"], case["h"], case["w"], case["co"],
-                                                         case["k"], s, p, 1)
-        _assert(golden.check(case["name"], "out", ac.forward(x, w, s, p)))
-        _assert(golden.check(case["name"], "grad_x", ac.backward_input(g, x, w, s, p)))
-        _assert(golden.check(case["name"], "grad_x", ac.backward_input(g, x, w, s, p, fast_clamp=True)))
+        assert lib.adder_b200_set_variant(2, variant) == 0
+        plan = _lib.describe_plan(2, *shape, 0)
+        assert "tma" not in plan and plan != default_plan or "warp-tile" not in default_plan, (plan, default_plan)
+        if variant == 1:
+            assert "warp-tile" not in plan, plan
         _assert(golden.check(case["name"], "grad_w", ac.backward_weight(g, x, w, s, p)))
+        gw_raw = ac.backward_weight(g, x, w, s, p, eta=0.0)
+        got_s, want_s = golden.pair(case["name"], "grad_w_unscaled", gw_raw)
+        scale = max(1.0, float(want_s.abs().max()))
+        _assert(O.compare("grad_w_unscaled/scale", got_s / scale, want_s / scale))
 
 
 def test_module_autograd_and_bias(ac):

@@ -50,9 +50,6 @@ def test_plans_are_launchable(op):
             assert "status=0" in plan, (shape, plan)
             threads = _field(plan, "threads")
             assert threads is not None and 32 <= threads <= 256 and threads % 32 == 0, (shape, plan)
-            if "persistent" in plan or "warp-tile" in plan:
-                assert 2 * (_field(plan, "smem") + 1024) <= 227 * 1024 or "grid=(%d," % _field(plan, "units") in plan \
-                    or _field(plan, "smem") <= 200 * 1024, (shape, plan)
             smem = _field(plan, "smem")
             if smem is not None:          # the one-thread-per-position kernels use static shared memory
                 assert smem <= SMEM_LIMIT, (shape, plan)
@@ -82,18 +79,12 @@ def test_special_case_kernels_are_chosen_where_they_apply():
 
 
 def test_chunking_does_not_depend_on_the_batch():
-    """The non-persistent kernels compute sub-batches with the same chunk boundaries (bitwise-equal results
-    per image whatever the batch size).  The persistent kernels do not promise that: how many thread groups
-    share a reduction depends on how much parallelism the whole batch offers, so their summation order is
-    fixed per geometry (run-to-run bitwise equal), not per image."""
-    with _lib.tuning() as tlib:
-        for op in range(3):
-            assert tlib.adder_b200_set_variant(op, 1) == 0
-        for op, key in ((0, "CK"), (1, "CKO")):
-            for shape in ((64, 8, 8, 64), (32, 16, 16, 32), (256, 14, 14, 256)):
-                ci, h, w, co = shape
-                values = {_field(_lib.describe_plan(op, n, ci, h, w, co, 3, 1, 1, 1), key) for n in (1, 2, 3, 8, 64, 256)}
-                assert len(values) == 1, (op, shape, values)
+    """Sub-batches must be computed with the same chunk boundaries (bitwise-equal results per image)."""
+    for op, key in ((0, "CK"), (1, "CKO")):
+        for shape in ((64, 8, 8, 64), (32, 16, 16, 32), (256, 14, 14, 256)):
+            ci, h, w, co = shape
+            values = {_field(_lib.describe_plan(op, n, ci, h, w, co, 3, 1, 1, 1), key) for n in (1, 2, 3, 8, 64, 256)}
+            assert len(values) == 1, (op, shape, values)
 
 
 def test_unsupported_geometry_is_reported_not_planned():
