@@ -54,7 +54,7 @@ RESNET20_LAYERS = [
 NCU_CAPTURE = "profiles/adder_kernels_c16to16_32x32_b256.txt"
 NCU_DRAM_BYTES = {"fwd": 16816384, "grad_x": 33628160, "grad_w": 33596672}
 ALGO_BYTES_16x16 = {"fwd": 33563648, "grad_x": 50340864, "grad_w": 33572864}
-KERNEL_NAMES = {"fwd": "adder_fwd_pipe_kernel", "grad_x": "adder_gx_pipe_kernel", "grad_w": "adder_gw_pipe_kernel"}
+KERNEL_NAMES = {"fwd": "adder_fwd_kernel", "grad_x": "adder_gx_kernel", "grad_w": "adder_gw_tma_kernel"}
 
 
 def triples(n, shape):

@@ -235,6 +235,17 @@ def network_fixture(ref_adder, module_name: str, ctor: str, batch: int, in_hw: i
     for k in grads:
         exact(grads_o[k], grads[k], f"{module_name} grad {k} (port)")
     lg64, loss64, grads64 = run(build_on(adder_unfold, module_name, ctor), torch.float64)
+    # the reference's self-noise: how far its own float32 gradients move under 1e-6 relative perturbations of
+    # the images (three draws) and between float32 and float64 (see resnet20_fixture)
+    noise = {k: (grads64[k] - v.double()).abs().max().item() for k, v in grads.items()}
+    clean = images
+    for j in range(3):
+        rng = np.random.default_rng(seed + 99 + j)
+        images = clean * t((1.0 + 1e-6 * rng.standard_normal(tuple(clean.shape))).astype(np.float32))
+        _, _, gp = run(build_on(adder_unfold, module_name, ctor), torch.float32)
+        for k, v in grads.items():
+            noise[k] = max(noise[k], (gp[k] - v).abs().max().item())
+    images = clean
     out = {"logits": lg.numpy(), "loss": np.float32(loss.item()), "logits64": lg64.to(torch.float32).numpy(),
            "loss64": np.float64(loss64.item()), "keys": np.array(list(grads.keys())),
            "batch": np.int64(batch), "in_hw": np.int64(in_hw), "classes": np.int64(classes), "seed": np.int64(seed)}
@@ -244,6 +255,7 @@ def network_fixture(ref_adder, module_name: str, ctor: str, batch: int, in_hw: i
         out[f"grad/{k}.val"] = val
         out[f"grad/{k}.sumsq"] = s2
         out[f"grad64/{k}.val"] = grads64[k].numpy().reshape(-1)[idx].astype(np.float32)
+        out[f"noise/{k}"] = np.float64(noise[k])
     return out
 
 

@@ -69,7 +69,7 @@ def check_step(z, logits, loss, named_grads, sampled: bool, max_anchored: int, l
         loss_tol += 2.0 * abs(want_loss - float(z["loss64"]))
     assert abs(float(loss) - want_loss) <= loss_tol, (float(loss), want_loss)
     failures, anchored, worst_name, worst_err, n = [], [], None, -1.0, 0
-    for k, g in named_grads:
+    for k, g in (named_grads or []):
         n += 1
         if sampled:
             idx = z[f"grad/{k}.idx"]
@@ -86,6 +86,8 @@ def check_step(z, logits, loss, named_grads, sampled: bool, max_anchored: int, l
             anchored.append(msg)
         if not ok:
             failures.append(msg)
+    if named_grads is None:
+        return
     log(f"    worst gradient tensor: {worst_name} max_abs_err={worst_err:.3e} "
         f"({n} tensors compared; {len(anchored)} needed more than the plain rule)")
     for m in anchored:

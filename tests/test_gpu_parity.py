@@ -137,7 +137,9 @@ def test_weight_gradient_kernel_families(case, variant, golden, ac):
     with _lib.tuning() as lib:
         assert lib.adder_b200_set_variant(2, variant) == 0
         plan = _lib.describe_plan(2, *shape, 0)
-        assert "tma" not in plan and plan != default_plan or "warp-tile" not in default_plan, (plan, default_plan)
+        assert "tma" not in plan, plan
+        if s == 1 and "tma" in default_plan:
+            assert plan != default_plan
         if variant == 1:
             assert "warp-tile" not in plan, plan
         _assert(golden.check(case["name"], "grad_w", ac.backward_weight(g, x, w, s, p)))

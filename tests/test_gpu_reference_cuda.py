@@ -26,7 +26,7 @@ ROOT = Path(__file__).resolve().parent.parent
 
 # (n, ci, co, h, w, k, stride, pad): K = ci*k*k, Co and P = n*ho*wo all multiples of 16
 SHAPES = [(8, 16, 16, 32, 32, 3, 1, 1), (4, 32, 32, 16, 16, 3, 1, 1), (4, 64, 64, 8, 8, 3, 1, 1),
-          (4, 16, 32, 32, 32, 3, 2, 1), (4, 16, 32, 32, 32, 1, 2, 0), (2, 64, 128, 14, 14, 1, 1, 0)]
+          (4, 16, 32, 32, 32, 3, 2, 1), (4, 16, 32, 32, 32, 1, 2, 0), (4, 64, 128, 14, 14, 1, 1, 0)]
 
 
 @pytest.fixture(scope="module")
