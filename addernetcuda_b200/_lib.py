@@ -45,6 +45,10 @@ SIGNATURES = {
     "adder_b200_batchnorm_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "adder_b200_batchnorm_forward": (c_int, [c_void_p] * 10 + [c_float, c_float, c_int, c_void_p, c_size_t,
                                              c_int, c_int, c_int, c_void_p]),
+    "adder_b200_forward_stat_slices": (c_int, [*_GEOM]),
+    "adder_b200_forward_with_stats": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, *_GEOM, c_void_p]),
+    "adder_b200_batchnorm_forward_from_stats": (c_int, [c_void_p, c_void_p, c_int] + [c_void_p] * 9 +
+                                                [c_float, c_float, c_int, c_int, c_int, c_int, c_void_p]),
     "adder_b200_batchnorm_backward": (c_int, [c_void_p] * 10 + [c_int, c_void_p, c_size_t, c_int, c_int, c_int,
                                               c_void_p]),
     "adder_b200_affine_forward": (c_int, [c_void_p] * 5 + [c_int, c_int, c_int, c_int, c_void_p]),

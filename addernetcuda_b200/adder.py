@@ -27,7 +27,7 @@ class _Adder2dNCHW(Function):
     """out = -sum|x_patch - w| with the reference's two surrogate gradients (adder.py:62-80)."""
 
     @staticmethod
-    def forward(ctx, x, w, stride, padding):
+    def forward(ctx, x, w, stride, padding, want_stats=False):
         # A data-parallel wrapper may attach `_grad_slot` to the parameter: a view into its flat
         # gradient bucket.  The weight-gradient kernel then writes the rescaled gradient there
         # directly, so no pack copy precedes the all-reduce.
@@ -36,23 +36,27 @@ class _Adder2dNCHW(Function):
         w = w.contiguous()
         ctx.save_for_backward(x, w)
         ctx.stride, ctx.padding = stride, padding
+        if want_stats:
+            out, st = adder_cuda.forward(x, w, stride, padding, stats=True)
+            ctx.mark_non_differentiable(st)
+            return out, st
         return adder_cuda.forward(x, w, stride, padding)
 
     @staticmethod
-    def backward(ctx, grad_out):
+    def backward(ctx, grad_out, *_unused):
         x, w = ctx.saved_tensors
         grad_out = grad_out.contiguous()
         gx = gw = None
         if ctx.needs_input_grad[0] and ctx.needs_input_grad[1]:
             gx, gw = adder_cuda.backward(grad_out, x, w, ctx.stride, ctx.padding, adder_cuda.ETA, FAST_CLAMP,
                                          out_w=ctx.grad_slot, overlap=OVERLAP_BACKWARD)
-            return gx, gw, None, None
+            return gx, gw, None, None, None
         if ctx.needs_input_grad[0]:
             gx = adder_cuda.backward_input(grad_out, x, w, ctx.stride, ctx.padding, FAST_CLAMP)
         if ctx.needs_input_grad[1]:
             gw = adder_cuda.backward_weight(grad_out, x, w, ctx.stride, ctx.padding, adder_cuda.ETA,
                                             out=ctx.grad_slot)
-        return gx, gw, None, None
+        return gx, gw, None, None, None
 
 
 def adder2d_function(X, W, stride=1, padding=0):
@@ -110,3 +114,11 @@ class adder2d(nn.Module):
         if self.bias:
             output = output + self.b.unsqueeze(0).unsqueeze(2).unsqueeze(3)
         return output
+
+    def forward_with_stats(self, x):
+        """`(forward(x), st)` where `st` holds the per-channel sums a following batch norm needs
+        (`adder_cuda.forward(..., stats=True)`), or None where the layer cannot provide them."""
+        if self.bias or not x.is_cuda:
+            return self.forward(x), None
+        out, st = _Adder2dNCHW.apply(x, self.adder, self.stride, self.padding, True)
+        return out, (st if st.shape[1] > 0 else None)

@@ -87,16 +87,30 @@ def _geom(x: torch.Tensor, w: torch.Tensor, stride: int, padding: int):
 
 # ---------------------------------------------------------------------------- fused NCHW path
 
-def forward(x: torch.Tensor, w: torch.Tensor, stride: int = 1, padding: int = 0) -> torch.Tensor:
-    """out[N,Co,Ho,Wo] = -sum |x_patch - w|: adder2d_function's forward (adder.py:22-41) in one kernel."""
+def forward(x: torch.Tensor, w: torch.Tensor, stride: int = 1, padding: int = 0, stats: bool = False):
+    """out[N,Co,Ho,Wo] = -sum |x_patch - w|: adder2d_function's forward (adder.py:22-41) in one kernel.
+
+    With `stats=True` returns `(out, st)`: `st` is a float64 tensor [Co, slices, 2] holding, per pixel
+    tile of the launch, the sum of each channel's outputs and of their squares - what the batch norm
+    after the layer (resnet20.py:28-29) needs, so that it does not have to read `out` twice.  `st` is
+    empty (0 slices) for the geometries whose kernel has no such epilogue."""
     _check(x, "x"); _check(w, "w")
     dev = _same_device(x, w)
     g = _geom(x, w, stride, padding)
     ho, wo = output_size(g[2], g[3], g[5], g[6], g[7])
     out = torch.empty((g[0], g[4], ho, wo), dtype=torch.float32, device=dev)
+    lib = _lib.load()
     with torch.cuda.device(dev):
-        _lib.check(_lib.load().adder_b200_forward(x.data_ptr(), w.data_ptr(), out.data_ptr(), *g, _stream(dev)),
+        slices = lib.adder_b200_forward_stat_slices(*g) if stats else 0
+        if slices > 0:
+            st = torch.empty((g[4], slices, 2), dtype=torch.float64, device=dev)
+            _lib.check(lib.adder_b200_forward_with_stats(x.data_ptr(), w.data_ptr(), out.data_ptr(), st.data_ptr(),
+                                                         slices, *g, _stream(dev)), "adder_b200_forward_with_stats")
+            return out, st
+        _lib.check(lib.adder_b200_forward(x.data_ptr(), w.data_ptr(), out.data_ptr(), *g, _stream(dev)),
                    "adder_b200_forward")
+    if stats:
+        return out, torch.empty((g[4], 0, 2), dtype=torch.float64, device=dev)
     return out
 
 

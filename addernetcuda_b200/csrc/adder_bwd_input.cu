@@ -40,7 +40,7 @@ __device__ __forceinline__ float gx_term(float wv, float xv) {
 // (PH, PW) in the shared-memory patch of g; later taps sit one row / one column before it.
 template <int KS, int RW, int RC, bool FAST, int PH, int PW>
 __device__ __forceinline__ void gx_taps_stride2(float (&acc)[RC][RW], const float (&xv)[RC][RW], const float* gch,
-                                                const float* wch, int row0, int col0, int pitch, int tcip) {
+                                                const float* wch, int row0, int col0, int pitch) {
 #pragma unroll
     for (int kh = PH; kh < KS; kh += 2) {
         const float* gr = gch + (row0 - (kh - PH) / 2) * pitch + col0;
@@ -50,7 +50,7 @@ __device__ __forceinline__ void gx_taps_stride2(float (&acc)[RC][RW], const floa
             float gv[RW];
 #pragma unroll
             for (int j = 0; j < RW; ++j) gv[j] = gp[j];
-            const float4 t = *reinterpret_cast<const float4*>(wch + (kh * KS + kw) * tcip);
+            const float4 t = *reinterpret_cast<const float4*>(wch + (kh * KS + kw) * RC);
             const float wv[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
             for (int cc = 0; cc < RC; ++cc)
@@ -60,7 +60,9 @@ __device__ __forceinline__ void gx_taps_stride2(float (&acc)[RC][RW], const floa
     }
 }
 
-// Weight slab of one output-channel chunk -> shared memory as [col][tap][TCIP] (input channel innermost).
+// Weight slab of one output-channel chunk -> shared memory as [col][input-channel quad][tap][4]: a thread's four
+// input channels of one tap are one 128-bit load, and the taps of a column sit at compile-time offsets from it
+// (no index arithmetic in the tap loops).  WCOL = TCI*KS*KS floats per column.
 // 3x3: thread (wgrp, wpr) owns the (input channel, tap) pairs wpr, wpr + WPP, ... and walks the output
 // channels wgrp, wgrp + wgroups, ...: the index arithmetic is done once per pair, and consecutive pairs
 // are consecutive in global memory.  1x1: the slab is [CKO][TCI]; a flat element loop measured faster.
@@ -74,7 +76,7 @@ __device__ __forceinline__ void gx_stage_weights(const GxArgs& a, float* wt, int
             a.d_tci.divmod(e, col, cil);
             const int co = coc0 + col, ci = ci0 + cil;
             const bool ok = (co < a.g.Co) & (ci < a.g.Ci);
-            cp_async4(wt + col * a.TCIP + cil, ok ? a.w + ((size_t)co * a.g.Ci + ci) : a.w, ok);
+            cp_async4(wt + col * a.WCOL + cil, ok ? a.w + ((size_t)co * a.g.Ci + ci) : a.w, ok);
         }
     } else if (wgrp < a.wgroups) {
         const int ncol = min(a.CKO, a.g.Co - coc0);
@@ -84,10 +86,10 @@ __device__ __forceinline__ void gx_stage_weights(const GxArgs& a, float* wt, int
             const int ci = ci0 + cil;
             const bool okc = ci < a.g.Ci;
             const float* src = a.w + ((size_t)coc0 * a.g.Ci + (okc ? ci : 0)) * KK + tap;
-            float* dst = wt + tap * a.TCIP + cil;
+            float* dst = wt + ((cil >> 2) * KK + tap) * 4 + (cil & 3);
             for (int col = wgrp; col < a.CKO; col += a.wgroups) {
                 const bool ok = okc & (col < ncol);
-                cp_async4(dst + col * KK * a.TCIP, ok ? src + (size_t)col * a.g.Ci * KK : a.w, ok);
+                cp_async4(dst + col * a.WCOL, ok ? src + (size_t)col * a.g.Ci * KK : a.w, ok);
             }
         }
     }
@@ -102,15 +104,15 @@ __device__ __forceinline__ void gx_scale_weights(const GxArgs& a, float* wt, int
         for (int e = tid; e < a.CKO * a.TCI; e += nthreads) {
             uint32_t col, cil;
             a.d_tci.divmod(e, col, cil);
-            float* p = wt + col * a.TCIP + cil;
+            float* p = wt + col * a.WCOL + cil;
             *p = fmaf(*p, 0.5f, 0.5f);
         }
     } else if (wgrp < a.wgroups) {
         for (int pr = wpr; pr < a.TCI * KK; pr += a.WPP) {
             uint32_t cil, tap;
             a.d_kk.divmod(pr, cil, tap);
-            float* p = wt + tap * a.TCIP + cil;
-            for (int col = wgrp; col < a.CKO; col += a.wgroups) p[col * KK * a.TCIP] = fmaf(p[col * KK * a.TCIP], 0.5f, 0.5f);
+            float* p = wt + ((cil >> 2) * KK + tap) * 4 + (cil & 3);
+            for (int col = wgrp; col < a.CKO; col += a.wgroups) p[col * a.WCOL] = fmaf(p[col * a.WCOL], 0.5f, 0.5f);
         }
     }
 }
@@ -240,16 +242,16 @@ __global__ void __launch_bounds__(256, MB) adder_gx_kernel(const GxArgs a) {
         if (active) {
             const int ncol = min(a.CKO, a.g.Co - c * a.CKO);
             const float* gimg = gs + img * a.pd.ROWS_PITCH;
-            const float* wt = Wt + (c & 1) * a.ws_stage + cig * RC;
+            const float* wt = Wt + (c & 1) * a.ws_stage + cig * (KK * RC);
+            const int goff_s1 = (int)ws * RW + ((int)hr + KS - 1) * a.pd.PITCH;
 #pragma unroll 1
             for (int col = 0; col < ncol; ++col) {
                 const float* gch = gimg + col * a.CH_STRIDE;
-                const float* wch = wt + col * KK * a.TCIP;
+                const float* wch = wt + col * a.WCOL;
                 if constexpr (S == 1) {
-                    const float* gcol = gch + ws * RW;
+                    const float* gr = gch + goff_s1;     // row of tap kh = 0; later taps sit one row up each
 #pragma unroll
-                    for (int kh = 0; kh < KS; ++kh) {
-                        const float* gr = gcol + ((int)hr + KS - 1 - kh) * a.pd.PITCH;
+                    for (int kh = 0; kh < KS; ++kh, gr -= a.pd.PITCH) {
                         float gv[RW + KS - 1];
                         load_run<RW + KS - 1, (RW % 4 == 0)>(gv, gr);
                         if constexpr (PACKED) {
@@ -259,7 +261,7 @@ __global__ void __launch_bounds__(256, MB) adder_gx_kernel(const GxArgs a) {
                             for (int i = 0; i < RW + KS - 1; ++i) g2[i] = pack2(gv[i], gv[i]);
 #pragma unroll
                             for (int kw = 0; kw < KS; ++kw) {
-                                const float4 t = *reinterpret_cast<const float4*>(wch + (kh * KS + kw) * a.TCIP);
+                                const float4 t = *reinterpret_cast<const float4*>(wch + (kh * KS + kw) * RC);
                                 const float wv[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
                                 for (int cc = 0; cc < RC; cc += 2)
@@ -271,7 +273,7 @@ __global__ void __launch_bounds__(256, MB) adder_gx_kernel(const GxArgs a) {
                         } else {
 #pragma unroll
                         for (int kw = 0; kw < KS; ++kw) {
-                            const float4 t = *reinterpret_cast<const float4*>(wch + (kh * KS + kw) * a.TCIP);
+                            const float4 t = *reinterpret_cast<const float4*>(wch + (kh * KS + kw) * RC);
                             const float wv[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
                             for (int cc = 0; cc < RC; ++cc)
@@ -286,10 +288,10 @@ __global__ void __launch_bounds__(256, MB) adder_gx_kernel(const GxArgs a) {
                     const int row0 = (hi + pad - ph) / 2 - go_r0;
                     const int col0 = q0 + ((int)pw + pad - pwp) / 2 - go_c0;
                     switch (ph * 2 + pwp) {     // uniform across a warp when the segments are ordered by class
-                        case 0: gx_taps_stride2<KS, RW, RC, FAST, 0, 0>(acc, xv, gch, wch, row0, col0, a.pd.PITCH, a.TCIP); break;
-                        case 1: gx_taps_stride2<KS, RW, RC, FAST, 0, 1>(acc, xv, gch, wch, row0, col0, a.pd.PITCH, a.TCIP); break;
-                        case 2: gx_taps_stride2<KS, RW, RC, FAST, 1, 0>(acc, xv, gch, wch, row0, col0, a.pd.PITCH, a.TCIP); break;
-                        default: gx_taps_stride2<KS, RW, RC, FAST, 1, 1>(acc, xv, gch, wch, row0, col0, a.pd.PITCH, a.TCIP); break;
+                        case 0: gx_taps_stride2<KS, RW, RC, FAST, 0, 0>(acc, xv, gch, wch, row0, col0, a.pd.PITCH); break;
+                        case 1: gx_taps_stride2<KS, RW, RC, FAST, 0, 1>(acc, xv, gch, wch, row0, col0, a.pd.PITCH); break;
+                        case 2: gx_taps_stride2<KS, RW, RC, FAST, 1, 0>(acc, xv, gch, wch, row0, col0, a.pd.PITCH); break;
+                        default: gx_taps_stride2<KS, RW, RC, FAST, 1, 1>(acc, xv, gch, wch, row0, col0, a.pd.PITCH); break;
                     }
                 } else {
 #pragma unroll
@@ -305,7 +307,7 @@ __global__ void __launch_bounds__(256, MB) adder_gx_kernel(const GxArgs a) {
                             float gv[RW];
 #pragma unroll
                             for (int j = 0; j < RW; ++j) gv[j] = gp[j];
-                            const float4 t = *reinterpret_cast<const float4*>(wch + (kh * KS + kw) * a.TCIP);
+                            const float4 t = *reinterpret_cast<const float4*>(wch + (kh * KS + kw) * RC);
                             const float wv[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
                             for (int cc = 0; cc < RC; ++cc)
@@ -509,18 +511,18 @@ __global__ void __launch_bounds__(256, 2) adder_gx_s2pair_kernel(const GxArgs a)
         if (active) {
             const int ncol = min(a.CKO, a.g.Co - c * a.CKO);
             const float* gimg = gs + img * a.pd.ROWS_PITCH;
-            const float* wt = Wt + (c & 1) * a.ws_stage + cig * RC;
+            const float* wt = Wt + (c & 1) * a.ws_stage + cig * (KK * RC);
 #pragma unroll 1
             for (int col = 0; col < ncol; ++col) {
                 const float* gch = gimg + col * a.CH_STRIDE;
-                const float* wch = wt + col * KK * a.TCIP;
+                const float* wch = wt + col * a.WCOL;
 #pragma unroll
                 for (int sg = 0; sg < NSEG; ++sg) {
                     switch (tapcls[sg]) {       // uniform across a warp
-                        case 0: gx_taps_stride2<KS, RW, RC, FAST, 0, 0>(acc[sg], xv[sg], gch, wch, row0v[sg], col0v[sg], a.pd.PITCH, a.TCIP); break;
-                        case 1: gx_taps_stride2<KS, RW, RC, FAST, 0, 1>(acc[sg], xv[sg], gch, wch, row0v[sg], col0v[sg], a.pd.PITCH, a.TCIP); break;
-                        case 2: gx_taps_stride2<KS, RW, RC, FAST, 1, 0>(acc[sg], xv[sg], gch, wch, row0v[sg], col0v[sg], a.pd.PITCH, a.TCIP); break;
-                        default: gx_taps_stride2<KS, RW, RC, FAST, 1, 1>(acc[sg], xv[sg], gch, wch, row0v[sg], col0v[sg], a.pd.PITCH, a.TCIP); break;
+                        case 0: gx_taps_stride2<KS, RW, RC, FAST, 0, 0>(acc[sg], xv[sg], gch, wch, row0v[sg], col0v[sg], a.pd.PITCH); break;
+                        case 1: gx_taps_stride2<KS, RW, RC, FAST, 0, 1>(acc[sg], xv[sg], gch, wch, row0v[sg], col0v[sg], a.pd.PITCH); break;
+                        case 2: gx_taps_stride2<KS, RW, RC, FAST, 1, 0>(acc[sg], xv[sg], gch, wch, row0v[sg], col0v[sg], a.pd.PITCH); break;
+                        default: gx_taps_stride2<KS, RW, RC, FAST, 1, 1>(acc[sg], xv[sg], gch, wch, row0v[sg], col0v[sg], a.pd.PITCH); break;
                     }
                 }
             }
@@ -637,7 +639,8 @@ static int plan_gx_n(const Geom& g, const TileHint& hint, GxPlan& p, int nseg) {
     const int cg_max = hint.cg > 0 ? hint.cg : (S > 1 ? 2 : (g.Ci >= 128 ? 8 : 4));   // stride > 1: more pixels per CTA, one tap class per warp
     a.CGI = ceil_div(g.Ci, RC) < cg_max ? ceil_div(g.Ci, RC) : cg_max;
     a.TCI = a.CGI * RC;
-    a.TCIP = a.TCI + 4;
+    a.TCIP = a.TCI;
+    a.WCOL = a.TCI * KS * KS;
     int segs_target = threads_target / a.CGI * nseg;
     if (segs_target < 1) segs_target = 1;
     const int class_px = ceil_div(g.W, S);                 // pixels of one column parity in a row
@@ -698,7 +701,7 @@ static int plan_gx_n(const Geom& g, const TileHint& hint, GxPlan& p, int nseg) {
     int cko = hint.ck > 0 ? hint.ck : (KS == 1 ? 64 : 16);
     if (cko > g.Co) cko = g.Co;
     while (cko > 1) {
-        const int need = 2 * (round_up(cko * ti_budget * pd.ROWS_PITCH, 4) + cko * KS * KS * a.TCIP) +
+        const int need = 2 * (round_up(cko * ti_budget * pd.ROWS_PITCH, 4) + cko * a.WCOL) +
                          (FAST ? ti_budget * pd.ROWS_PITCH : 0) + RC * RW * threads_full * nseg;
         if (need <= budget_floats) break;
         --cko;
@@ -707,7 +710,7 @@ static int plan_gx_n(const Geom& g, const TileHint& hint, GxPlan& p, int nseg) {
     a.CKO = cko;
     pd.CH = cko;
     a.gs_stage = round_up(cko * a.CH_STRIDE, 4);
-    a.ws_stage = cko * KS * KS * a.TCIP;
+    a.ws_stage = cko * a.WCOL;
     const int nchunks = ceil_div(g.Co, cko);
     a.nstages = nchunks > 1 ? 2 : 1;
     // running totals in shared memory only where the kernels use them (several chunks, or the 1x1 kernels)

@@ -40,7 +40,7 @@ struct GwPipeArgs {
     PatchDims pdx;       // haloed input patch of one item: [CI_T][XROWS][XP], channel stride XCH
     PatchDims pdg;       // tile of g of one item:          [CO_T][TH][GP],    channel stride GCH
     int TH, SPR, PR, PW, OT, OTi, CO_T, CI_T, XCH, GCH, XP, GP;
-    int xs_stage, stage_floats, splits, n_ci_blocks, g_quads, tpc, row_quantum, dbg;
+    int xs_stage, stage_floats, splits, n_ci_blocks, g_quads, tpc, row_quantum;
     long long rows_total;
     FastDiv d_ho, d_pw, d_ot, d_oti, d_ci_blocks, d_gquads, d_tpc, d_kk_ci;
 };
@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(GWP_WARPS * 32, 2) adder_gw_pipe_kernel(const 
         __syncthreads();          // this item has landed for everyone, and everyone is done with the previous one
         if (cur_f < R1) {
             int n, r0;
-            if (!(a.dbg & 1)) fill(cur_f, stage ^ 1);
+            fill(cur_f, stage ^ 1);
             cur_f += item_rows(cur_f, n, r0);
         }
         cp_async_commit();
@@ -158,7 +158,7 @@ __global__ void __launch_bounds__(GWP_WARPS * 32, 2) adder_gw_pipe_kernel(const 
                 }
             }
         }
-        if (do_gsum && (int)gs_ch < a.CO_T && !(a.dbg & 2)) {
+        if (do_gsum && (int)gs_ch < a.CO_T) {
             // strip sums of g over the item's valid rows (fixed order: the result does not depend on scheduling)
             const float* gch = Gs + gs_ch * a.GCH;
             if (RW % 4 == 0) {
@@ -181,17 +181,6 @@ __global__ void __launch_bounds__(GWP_WARPS * 32, 2) adder_gw_pipe_kernel(const 
     cp_async_wait<0>();
     __syncthreads();              // the stages are free: they become the exchange buffer
 
-    if (a.dbg & 4) {
-        float sdbg = 0.f;
-#pragma unroll
-        for (int m = 0; m < RM; ++m)
-#pragma unroll
-            for (int c = 0; c < RC; ++c)
-#pragma unroll
-                for (int t = 0; t < KK; ++t) sdbg += acc[m][c][t];
-        if (sdbg == 123.456f) a.part[0] = sdbg;
-        return;
-    }
     // Every warp parks its accumulators as [warp][e][lane]; then all threads walk the CTA's block of the
     // gradient in global-memory order, add the PS pixel shares of each element and write it to the slice.
     {
@@ -339,7 +328,6 @@ static GwPipePlan plan_gw_pipe_t(const Geom& g, const TileHint& hint) {
     if (splits > quanta) splits = quanta;
     if (splits < 1) splits = 1;
     a.splits = (int)splits;
-    a.dbg = hint.threads;
     a.tpc = GWP_WARPS * 32 / a.CO_T;
     if (a.tpc > 32) a.tpc = 32;
     if (a.tpc < 1) a.tpc = 1;

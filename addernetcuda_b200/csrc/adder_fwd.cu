@@ -68,16 +68,20 @@ __global__ void __launch_bounds__(256, 2) adder_fwd_kernel(const FwdArgs a) {
         float* wsm = Ws + stage * a.ws_stage;
         const int kbase = ci0 * KK;
         const int kk_lim = a.CK * KK;
+        // slab layout [ci][channel group][tap][RM]: a thread's RM channels of one tap are 128-bit loads, and the
+        // taps of one input channel sit at compile-time offsets from each other
         for (int e = tid; e < w_elems; e += nthreads) {
             uint32_t t, col, kkb;
             const int kk8 = e & 7;
             t = e >> 3;
             a.d_tm.divmod(t, kkb, col);
             const int kk = kkb * 8 + kk8;
+            if (kk >= kk_lim) continue;
             const int co = co0 + col;
-            const bool ok = (co < a.g.Co) & (kk < kk_lim) & (kbase + kk < K);
+            const bool ok = (co < a.g.Co) & (kbase + kk < K);
             const float* src = ok ? a.w + ((size_t)co * K + kbase + kk) : a.w;
-            cp_async4(wsm + kk * a.TMP + col, src, ok);
+            const int cil = kk / KK, tap = kk - cil * KK;
+            cp_async4(wsm + cil * a.WCIL + ((col / RM) * KK + tap) * RM + (col % RM), src, ok);
         }
     };
 
@@ -93,15 +97,15 @@ __global__ void __launch_bounds__(256, 2) adder_fwd_kernel(const FwdArgs a) {
         }
         __syncthreads();
         if (active) {
-            const float* xs = Xs + (c & 1) * a.xs_stage + xoff;
-            const float* wsm = Ws + (c & 1) * a.ws_stage + cg * RM;
+            const float* xc = Xs + (c & 1) * a.xs_stage + xoff;
+            const float* wc = Ws + (c & 1) * a.ws_stage + cg * (KK * RM);
             const int nch = min(a.CK, a.g.Ci - c * a.CK);
 #pragma unroll 1
-            for (int cil = 0; cil < nch; ++cil) {
+            for (int cil = 0; cil < nch; ++cil, xc += a.CH_STRIDE, wc += a.WCIL) {
+                const float* xr = xc;
 #pragma unroll
-                for (int kh = 0; kh < KS; ++kh) {
+                for (int kh = 0; kh < KS; ++kh, xr += a.PITCH) {
                     float xv[XW];
-                    const float* xr = xs + cil * a.CH_STRIDE + kh * a.PITCH;
                     load_run<XW, (RW % 4 == 0)>(xv, xr);
 #if ADDER_FWD_PACKED
                     uint64_t nx2[XW];
@@ -110,7 +114,7 @@ __global__ void __launch_bounds__(256, 2) adder_fwd_kernel(const FwdArgs a) {
 #endif
 #pragma unroll
                     for (int kw = 0; kw < KS; ++kw) {
-                        const float* wr = wsm + (cil * KK + kh * KS + kw) * a.TMP;
+                        const float* wr = wc + (kh * KS + kw) * RM;
                         float wv[RM];
 #pragma unroll
                         for (int m4 = 0; m4 < RM; m4 += 4) {
@@ -143,24 +147,60 @@ __global__ void __launch_bounds__(256, 2) adder_fwd_kernel(const FwdArgs a) {
         __syncthreads();
     }
 
-    if (!active) return;
     const int n = n0 + img, ho = ho0 + hr, wo0 = wo_t0 + ws * RW;
-    if (n >= a.g.N || ho >= a.g.Ho || wo0 >= a.g.Wo) return;
-    const int HoWo = a.g.Ho * a.g.Wo;
+    const bool valid = active && n < a.g.N && ho < a.g.Ho && wo0 < a.g.Wo;
+    if (valid) {
+        const int HoWo = a.g.Ho * a.g.Wo;
 #pragma unroll
-    for (int m = 0; m < RM; ++m) {
-        const int co = co0 + cg * RM + m;
-        if (co >= a.g.Co) break;
-        float* o = a.out + ((size_t)(n * a.g.Co + co) * HoWo + ho * a.g.Wo + wo0);
-        if (RW % 4 == 0 && a.vec_store) {
+        for (int m = 0; m < RM; ++m) {
+            const int co = co0 + cg * RM + m;
+            if (co >= a.g.Co) break;
+            float* o = a.out + ((size_t)(n * a.g.Co + co) * HoWo + ho * a.g.Wo + wo0);
+            if (RW % 4 == 0 && a.vec_store) {
 #pragma unroll
-            for (int j = 0; j < RW; j += 4)
-                *reinterpret_cast<float4*>(o + j) = make_float4(-acc[m][j], -acc[m][j + 1], -acc[m][j + 2], -acc[m][j + 3]);
-        } else {
+                for (int j = 0; j < RW; j += 4)
+                    *reinterpret_cast<float4*>(o + j) = make_float4(-acc[m][j], -acc[m][j + 1], -acc[m][j + 2], -acc[m][j + 3]);
+            } else {
 #pragma unroll
-            for (int j = 0; j < RW; ++j)
-                if (wo0 + j < a.g.Wo) o[j] = -acc[m][j];
+                for (int j = 0; j < RW; ++j)
+                    if (wo0 + j < a.g.Wo) o[j] = -acc[m][j];
+            }
         }
+    }
+    if (a.stats == nullptr) return;
+
+    // Batch-norm statistics of this pixel tile: for each of the CTA's channels the sum of its outputs and of
+    // their squares.  A thread adds its (at most RW) values in fp32; everything after that is double, in a
+    // fixed order, so the slices can be combined without cancellation although no pivot is subtracted.
+    float2* st = reinterpret_cast<float2*>(smem);           // [TM][SEGS]; the stages are free after the last barrier
+    if (active) {
+#pragma unroll
+        for (int m = 0; m < RM; ++m) {
+            float s = 0.f, q = 0.f;
+            if (valid) {
+#pragma unroll
+                for (int j = 0; j < RW; ++j)
+                    if (wo0 + j < a.g.Wo) { s -= acc[m][j]; q = fmaf(acc[m][j], acc[m][j], q); }
+            }
+            st[(cg * RM + m) * a.SEGS + seg] = make_float2(s, q);
+        }
+    }
+    __syncthreads();
+    const int tpc = a.stat_tpc;                             // power of two <= 32: the lanes of one channel sit in one warp
+    if ((tid & ~31) >= a.TM * tpc) return;                  // whole warps only: the shuffles below need every lane
+    const int ch = tid / tpc, l = tid - ch * tpc;
+    double ds = 0.0, dq = 0.0;
+    if (ch < a.TM) {
+        const float2* row = st + ch * a.SEGS;
+        for (int e = l; e < a.SEGS; e += tpc) { const float2 v = row[e]; ds += (double)v.x; dq += (double)v.y; }
+    }
+    for (int off = tpc >> 1; off > 0; off >>= 1) {
+        ds += __shfl_xor_sync(0xffffffffu, ds, off);
+        dq += __shfl_xor_sync(0xffffffffu, dq, off);
+    }
+    if (l == 0 && ch < a.TM && co0 + ch < a.g.Co) {
+        double* o = a.stats + ((size_t)(co0 + ch) * a.stat_slices + blockIdx.x) * 2;
+        o[0] = ds; o[1] = dq;
     }
 }
 
@@ -255,7 +295,7 @@ static int plan_fwd_t(const Geom& g, const float* out, const TileHint& hint, Fwd
     int ck = hint.ck > 0 ? hint.ck : (KS == 1 ? 32 : 16);
     if (ck > g.Ci) ck = g.Ci;
     while (ck > 1) {
-        const int need = 2 * (round_up(ck * ti_budget * a.ROWS_PITCH, 4) + round_up(ck * KS * KS, 8) * a.TMP);
+        const int need = 2 * (round_up(ck * ti_budget * a.ROWS_PITCH, 4) + ck * KS * KS * a.TM);
         if (need <= budget_floats) break;
         --ck;
     }
@@ -264,9 +304,15 @@ static int plan_fwd_t(const Geom& g, const float* out, const TileHint& hint, Fwd
     a.pd.CH = ck;
     a.wkk_pad = round_up(a.CK * KS * KS, 8);
     a.xs_stage = round_up(a.CK * a.CH_STRIDE, 4);
-    a.ws_stage = a.wkk_pad * a.TMP;
-    const size_t smem = (size_t)2 * (a.xs_stage + a.ws_stage) * sizeof(float);
+    a.WCIL = a.TM * KS * KS;
+    a.ws_stage = a.CK * a.WCIL;
+    size_t smem = (size_t)2 * (a.xs_stage + a.ws_stage) * sizeof(float);
+    const size_t stat_bytes = (size_t)a.TM * a.SEGS * sizeof(float2);   // the statistics epilogue reuses the stages
+    if (smem < stat_bytes) smem = stat_bytes;
     p.smem = smem;
+    a.stats = nullptr; a.stat_slices = 0;
+    a.stat_tpc = 32;
+    while (a.stat_tpc > 1 && a.TM * a.stat_tpc > threads) a.stat_tpc >>= 1;
     if (smem > 200 * 1024) return ADDER_ERR_UNSUPPORTED;
     a.tiles_h = ceil_div(g.Ho, a.TH);
     a.tiles_w = ceil_div(spr_full, a.SPR);
@@ -287,11 +333,15 @@ static int plan_fwd_t(const Geom& g, const float* out, const TileHint& hint, Fwd
 
 template <int KS, int S, int RW, int RM>
 static int launch_fwd_t(const Geom& g, const float* x, const float* w, float* out, const TileHint& hint,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, double* stats, int stat_slices) {
     FwdPlan p;
     const int st = plan_fwd_t<KS, S, RW, RM>(g, out, hint, p);
     if (st != ADDER_OK) return st;
     p.a.x = x; p.a.w = w; p.a.out = out;
+    if (stats != nullptr) {
+        if ((long long)stat_slices != p.gx || p.a.TM * p.a.stat_tpc > p.threads) return ADDER_ERR_WORKSPACE;
+        p.a.stats = stats; p.a.stat_slices = stat_slices;
+    }
     auto kern = adder_fwd_kernel<KS, S, RW, RM>;
     const int se = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), p.smem);
     if (se != ADDER_OK) return se;
@@ -350,12 +400,29 @@ int describe_fwd(const Geom& g, const TileHint& hint, char* buf, size_t n) {
     return ADDER_OK;
 }
 
-int launch_fwd(const Geom& g, const float* x, const float* w, float* out, const TileHint& hint,
-               cudaStream_t stream) {
-    if (hint.is_default() && pointwise_applicable(g)) return launch_pointwise_fwd(g, x, w, out, stream);
+int fwd_stat_slices(const Geom& g, const TileHint& hint) {
+    if (hint.is_default() && pointwise_applicable(g)) return 0;
     int rw = 8, rm = 8;
     choose_fwd_tile(g, hint, rw, rm);
-#define ADDER_FWD_LAUNCH(KS_, S_, RW_, RM_) return launch_fwd_t<KS_, S_, RW_, RM_>(g, x, w, out, hint, stream);
+    FwdPlan p;
+    int st = ADDER_ERR_UNSUPPORTED;
+#define ADDER_FWD_PLAN(KS_, S_, RW_, RM_) st = plan_fwd_t<KS_, S_, RW_, RM_>(g, nullptr, hint, p);
+    ADDER_FWD_DISPATCH(ADDER_FWD_PLAN)
+#undef ADDER_FWD_PLAN
+    if (st != ADDER_OK || p.a.TM * p.a.stat_tpc > p.threads || p.gx > (1 << 20)) return 0;
+    return (int)p.gx;
+}
+
+int launch_fwd(const Geom& g, const float* x, const float* w, float* out, const TileHint& hint,
+               cudaStream_t stream, double* stats, int stat_slices) {
+    if (hint.is_default() && pointwise_applicable(g)) {
+        if (stats != nullptr) return ADDER_ERR_UNSUPPORTED;
+        return launch_pointwise_fwd(g, x, w, out, stream);
+    }
+    int rw = 8, rm = 8;
+    choose_fwd_tile(g, hint, rw, rm);
+#define ADDER_FWD_LAUNCH(KS_, S_, RW_, RM_) \
+    return launch_fwd_t<KS_, S_, RW_, RM_>(g, x, w, out, hint, stream, stats, stat_slices);
     ADDER_FWD_DISPATCH(ADDER_FWD_LAUNCH)
 #undef ADDER_FWD_LAUNCH
     return ADDER_ERR_UNSUPPORTED;

@@ -133,6 +133,24 @@ int adder_b200_forward(const float* x, const float* w, float* out, int n, int ci
     return launch_fwd(g, x, w, out, current_hint(0), static_cast<cudaStream_t>(stream));
 }
 
+int adder_b200_forward_stat_slices(int n, int ci, int h, int wd, int co, int k, int stride, int pad) {
+    Geom g;
+    if (make_geom(n, ci, h, wd, co, k, stride, pad, &g) != ADDER_OK || n == 0) return 0;
+    return fwd_stat_slices(g, current_hint(0));
+}
+
+int adder_b200_forward_with_stats(const float* x, const float* w, float* out, double* stats, int stat_slices, int n,
+                                  int ci, int h, int wd, int co, int k, int stride, int pad, void* stream) {
+    Geom g;
+    const int st = make_geom(n, ci, h, wd, co, k, stride, pad, &g);
+    if (st != ADDER_OK) return st;
+    if (n == 0) return ADDER_ERR_BAD_SHAPE;      // an empty batch has no statistics
+    if (x == nullptr || w == nullptr || out == nullptr || stats == nullptr) return ADDER_ERR_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(stats) & 15) != 0) return ADDER_ERR_ALIGNMENT;
+    if (stat_slices <= 0 || stat_slices != fwd_stat_slices(g, current_hint(0))) return ADDER_ERR_WORKSPACE;
+    return launch_fwd(g, x, w, out, current_hint(0), static_cast<cudaStream_t>(stream), stats, stat_slices);
+}
+
 int adder_b200_backward_input(const float* grad_out, const float* x, const float* w, float* grad_x, int n, int ci,
                               int h, int wd, int co, int k, int stride, int pad, int flags, void* stream) {
     Geom g;

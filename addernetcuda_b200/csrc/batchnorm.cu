@@ -79,7 +79,9 @@ struct BnFwdArgs {
     const float* y; const float* gamma; const float* beta; const float* residual;
     float* z; float* save_mean; float* save_invstd; float* running_mean; float* running_var;
     long long* num_batches;   // optional counter (nn.BatchNorm2d.num_batches_tracked), incremented once per call
-    const double* part;
+    const double* part;       // [C][nparts][2]
+    int nparts;               // slices per channel in `part`
+    int pivoted;              // 1: sums of (y - y[0,c,0]) from bn_stats_kernel; 0: plain sums from the forward adder kernel
     float eps, momentum;
     int relu;
 };
@@ -89,13 +91,15 @@ struct BnFwdArgs {
 __global__ void __launch_bounds__(BN_THREADS) bn_apply_kernel(BnFwdArgs a, BnGeom g) {
     const int c = blockIdx.y, sp = blockIdx.x;
     __shared__ float s_mean, s_invstd;
+    double s = 0.0, q = 0.0;
+    for (int k = threadIdx.x; k < a.nparts; k += BN_THREADS) {
+        const double2 v = *reinterpret_cast<const double2*>(a.part + ((size_t)c * a.nparts + k) * 2);
+        s += v.x;
+        q += v.y;
+    }
+    block_sum2(s, q);
     if (threadIdx.x == 0) {
-        double s = 0.0, q = 0.0;
-        for (int k = 0; k < g.splits; ++k) {
-            s += a.part[((size_t)c * g.splits + k) * 2];
-            q += a.part[((size_t)c * g.splits + k) * 2 + 1];
-        }
-        const double pivot = (double)__ldg(a.y + (size_t)c * g.HW);
+        const double pivot = a.pivoted ? (double)__ldg(a.y + (size_t)c * g.HW) : 0.0;
         const double m1 = s / g.M;
         double var = q / g.M - m1 * m1;
         if (var < 0.0) var = 0.0;
@@ -326,28 +330,54 @@ size_t adder_b200_batchnorm_workspace_bytes(int n, int c, int hw) {
     return (size_t)c * g.splits * 2 * sizeof(double);
 }
 
-int adder_b200_batchnorm_forward(const float* y, const float* gamma, const float* beta, const float* residual,
-                                 float* z, float* save_mean, float* save_invstd, float* running_mean,
-                                 float* running_var, long long* num_batches_tracked, float eps, float momentum,
-                                 int relu, void* workspace, size_t workspace_bytes, int n, int c, int hw,
-                                 void* stream) {
+static int bn_forward(const float* y, const double* stats, int stat_slices, const float* gamma, const float* beta,
+                      const float* residual, float* z, float* save_mean, float* save_invstd, float* running_mean,
+                      float* running_var, long long* num_batches_tracked, float eps, float momentum, int relu,
+                      void* workspace, size_t workspace_bytes, int n, int c, int hw, void* stream) {
     BnGeom g;
     const int st = bn_geom(n, c, hw, &g);
     if (st != ADDER_OK) return st;
     if (!y || !gamma || !beta || !z || !save_mean || !save_invstd) return ADDER_ERR_NULL_POINTER;
     if ((running_mean == nullptr) != (running_var == nullptr)) return ADDER_ERR_NULL_POINTER;
-    if (workspace == nullptr || workspace_bytes < (size_t)c * g.splits * 2 * sizeof(double)) return ADDER_ERR_WORKSPACE;
-    if ((reinterpret_cast<uintptr_t>(workspace) & 15) != 0) return ADDER_ERR_ALIGNMENT;
     if (hw % 4 == 0 && (((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(z) |
                           reinterpret_cast<uintptr_t>(residual)) & 15) != 0)) return ADDER_ERR_ALIGNMENT;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    double* part = static_cast<double*>(workspace);
     const dim3 grid(g.splits, c);
-    bn_stats_kernel<<<grid, BN_THREADS, 0, s>>>(y, g, part);
     BnFwdArgs a{y, gamma, beta, residual, z, save_mean, save_invstd, running_mean, running_var, num_batches_tracked,
-                part, eps, momentum, relu};
+                nullptr, 0, 0, eps, momentum, relu};
+    if (stats != nullptr) {
+        if (stat_slices <= 0) return ADDER_ERR_BAD_SHAPE;
+        if ((reinterpret_cast<uintptr_t>(stats) & 15) != 0) return ADDER_ERR_ALIGNMENT;
+        a.part = stats; a.nparts = stat_slices; a.pivoted = 0;
+        bn_apply_kernel<<<grid, BN_THREADS, 0, s>>>(a, g);
+        return launched();
+    }
+    if (workspace == nullptr || workspace_bytes < (size_t)c * g.splits * 2 * sizeof(double)) return ADDER_ERR_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 15) != 0) return ADDER_ERR_ALIGNMENT;
+    double* part = static_cast<double*>(workspace);
+    bn_stats_kernel<<<grid, BN_THREADS, 0, s>>>(y, g, part);
+    a.part = part; a.nparts = g.splits; a.pivoted = 1;
     bn_apply_kernel<<<grid, BN_THREADS, 0, s>>>(a, g);
     return launched(2);
+}
+
+int adder_b200_batchnorm_forward(const float* y, const float* gamma, const float* beta, const float* residual,
+                                 float* z, float* save_mean, float* save_invstd, float* running_mean,
+                                 float* running_var, long long* num_batches_tracked, float eps, float momentum,
+                                 int relu, void* workspace, size_t workspace_bytes, int n, int c, int hw,
+                                 void* stream) {
+    return bn_forward(y, nullptr, 0, gamma, beta, residual, z, save_mean, save_invstd, running_mean, running_var,
+                      num_batches_tracked, eps, momentum, relu, workspace, workspace_bytes, n, c, hw, stream);
+}
+
+int adder_b200_batchnorm_forward_from_stats(const float* y, const double* stats, int stat_slices, const float* gamma,
+                                            const float* beta, const float* residual, float* z, float* save_mean,
+                                            float* save_invstd, float* running_mean, float* running_var,
+                                            long long* num_batches_tracked, float eps, float momentum, int relu, int n,
+                                            int c, int hw, void* stream) {
+    if (stats == nullptr) return ADDER_ERR_NULL_POINTER;
+    return bn_forward(y, stats, stat_slices, gamma, beta, residual, z, save_mean, save_invstd, running_mean,
+                      running_var, num_batches_tracked, eps, momentum, relu, nullptr, 0, n, c, hw, stream);
 }
 
 int adder_b200_batchnorm_backward(const float* dz, const float* y, const float* z, const float* gamma,

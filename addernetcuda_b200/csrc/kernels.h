@@ -30,7 +30,9 @@ struct FwdArgs {
     float* out;
     int TI, TH, SPR, SEGS, CG, TM, TMP, CK;
     int IN_ROWS, IN_COLS, PITCH, ROWS_PITCH, CH_STRIDE;
-    int xs_stage, ws_stage, wkk_pad, tiles_h, tiles_w, vec_store;
+    int xs_stage, ws_stage, wkk_pad, WCIL, tiles_h, tiles_w, vec_store;
+    double* stats;       // optional [Co][stat_slices][2]: per pixel tile, the sum of its outputs and of their squares
+    int stat_slices, stat_tpc;   // slices = pixel tiles of the launch; tpc = threads that share one channel's reduction
     PatchDims pd;        // haloed input patch staged per input-channel chunk
     FastDiv d_tiles_h, d_tiles_w, d_segs, d_spr, d_th, d_tm;
 };
@@ -42,7 +44,7 @@ struct GxArgs {
     const float* w;      // [Co,Ci,k,k]
     float* gx;           // [N,Ci,H,W]
     PatchDims pd;        // patch of g staged per output-channel chunk
-    int TI, TH, SPRC, SPR, SEGS, CGI, TCI, TCIP, CKO, CH_STRIDE;
+    int TI, TH, SPRC, SPR, SEGS, CGI, TCI, TCIP, WCOL, CKO, CH_STRIDE;
     int gs_stage, ws_stage, g1_size, tiles_h, tiles_w, accumulate, class_major;
     FastDiv d_tiles_h, d_tiles_w, d_segs, d_spr, d_sprc, d_th, d_ths, d_ti, d_wpp, d_kk, d_tci;
     int vec_io;          // x is read and grad_x written as aligned quads
@@ -94,7 +96,11 @@ inline int launched(int n = 1) {
 // the device's opt-in maximum, and remembered; later calls cost a lock and a table lookup.
 int ensure_dynamic_smem(const void* kernel, size_t bytes);
 
-int launch_fwd(const Geom& g, const float* x, const float* w, float* out, const TileHint& hint, cudaStream_t s);
+int launch_fwd(const Geom& g, const float* x, const float* w, float* out, const TileHint& hint, cudaStream_t s,
+               double* stats = nullptr, int stat_slices = 0);
+// Number of per-channel statistic slices the forward kernel of this geometry writes (one per pixel tile);
+// 0 when that kernel has no fused statistics.
+int fwd_stat_slices(const Geom& g, const TileHint& hint);
 int launch_gx(const Geom& g, const float* gout, const float* x, const float* w, float* gx, int fast,
               int accumulate, const TileHint& hint, cudaStream_t s);
 size_t gw_workspace_bytes(const Geom& g, const TileHint& hint);

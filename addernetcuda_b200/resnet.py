@@ -40,6 +40,22 @@ def _bn_act(bn, y, residual=None, relu=False):
     return torch.relu(out) if relu else out
 
 
+def _conv_bn_act(conv, bn, x, residual=None, relu=False):
+    """relu?(bn(conv(x)) + residual?).  An adder layer followed by a FusedBatchNorm2d in training mode hands
+    the batch statistics over from its own epilogue, so the normalisation reads the layer's output once."""
+    if (bn.__class__.__name__ == "FusedBatchNorm2d" and bn.training and x.is_cuda and x.dtype == torch.float32
+            and hasattr(conv, "forward_with_stats")):
+        y, st = conv.forward_with_stats(x)
+        return bn(y, residual=residual, relu=relu, stats=st)
+    return _bn_act(bn, conv(x), residual=residual, relu=relu)
+
+
+def _shortcut(downsample, x):
+    if isinstance(downsample, nn.Sequential) and len(downsample) == 2:
+        return _conv_bn_act(downsample[0], downsample[1], x)
+    return downsample(x)
+
+
 class BasicBlock(nn.Module):
     """conv3x3-BN-ReLU-conv3x3-BN + shortcut, ReLU (resnet20.py:12-41)."""
     expansion = 1
@@ -55,9 +71,9 @@ class BasicBlock(nn.Module):
         self.stride = stride
 
     def forward(self, x):
-        out = _bn_act(self.bn1, self.conv1(x), relu=True)
-        res = x if self.downsample is None else self.downsample(x)
-        return _bn_act(self.bn2, self.conv2(out), residual=res, relu=True)
+        out = _conv_bn_act(self.conv1, self.bn1, x, relu=True)
+        res = x if self.downsample is None else _shortcut(self.downsample, x)
+        return _conv_bn_act(self.conv2, self.bn2, out, residual=res, relu=True)
 
 
 class Bottleneck(nn.Module):
@@ -77,10 +93,10 @@ class Bottleneck(nn.Module):
         self.stride = stride
 
     def forward(self, x):
-        out = _bn_act(self.bn1, self.conv1(x), relu=True)
-        out = _bn_act(self.bn2, self.conv2(out), relu=True)
-        res = x if self.downsample is None else self.downsample(x)
-        return _bn_act(self.bn3, self.conv3(out), residual=res, relu=True)
+        out = _conv_bn_act(self.conv1, self.bn1, x, relu=True)
+        out = _conv_bn_act(self.conv2, self.bn2, out, relu=True)
+        res = x if self.downsample is None else _shortcut(self.downsample, x)
+        return _conv_bn_act(self.conv3, self.bn3, out, residual=res, relu=True)
 
 
 class _ResNet(nn.Module):

@@ -162,7 +162,25 @@ ADDER_API int adder_b200_batchnorm_forward(const float* y, const float* gamma, c
                                            float* running_mean, float* running_var, long long* num_batches_tracked,
                                            float eps, float momentum, int relu, void* workspace,
                                            size_t workspace_bytes, int n, int c, int hw, void* stream);
-/* Backward of the above: dz is the gradient of z; with relu != 0 it is first masked by z > 0 (z: the
+/* The same layer pair with the statistics pass folded into the adder layer that produces y
+ * (resnet20.py:28-29: conv1 then bn1).  adder_b200_forward_with_stats is adder_b200_forward that also
+ * writes, for every output channel and every pixel tile of the launch, the sum of the tile's outputs and
+ * of their squares in double precision: stats[co][stat_slices][2] (16-byte aligned), stat_slices =
+ * adder_b200_forward_stat_slices(same geometry), which is 0 for the geometries whose forward kernel has
+ * no such epilogue (use the two calls above for those).  adder_b200_batchnorm_forward_from_stats then
+ * normalises y from those slices without reading y a first time; slices are added in index order, so
+ * the result is deterministic. */
+ADDER_API int adder_b200_forward_stat_slices(int n, int ci, int h, int wd, int co, int k, int stride, int pad);
+ADDER_API int adder_b200_forward_with_stats(const float* x, const float* w, float* out, double* stats, int stat_slices,
+                                            int n, int ci, int h, int wd, int co, int k, int stride, int pad,
+                                            void* stream);
+ADDER_API int adder_b200_batchnorm_forward_from_stats(const float* y, const double* stats, int stat_slices,
+                                                      const float* gamma, const float* beta, const float* residual,
+                                                      float* z, float* save_mean, float* save_invstd,
+                                                      float* running_mean, float* running_var,
+                                                      long long* num_batches_tracked, float eps, float momentum,
+                                                      int relu, int n, int c, int hw, void* stream);
+/* Backward of batch normalisation: dz is the gradient of z; with relu != 0 it is first masked by z > 0 (z: the
  * forward output).  Outputs: dy, dgamma[c], dbeta[c] and, when dresidual != NULL, the gradient of the
  * residual input (= the masked dz). */
 ADDER_API int adder_b200_batchnorm_backward(const float* dz, const float* y, const float* z, const float* gamma,
