@@ -59,9 +59,33 @@ class _Adder2dNCHW(Function):
         return gx, gw, None, None, None
 
 
-def adder2d_function(X, W, stride=1, padding=0):
-    """Same contract as adder.py:22-41: X[N,Ci,H,W], W[Co,Ci,k,k] -> [N,Co,Ho,Wo], differentiable."""
-    return _Adder2dNCHW.apply(X, W, stride, padding)
+def _fused_geometry(W, stride, padding, dilation) -> bool:
+    """The geometries the fused NCHW kernels are built for: square 1x1 / 3x3 kernels, stride 1 or 2."""
+    return (W.dim() == 4 and W.shape[2] == W.shape[3] and W.shape[2] in (1, 3) and isinstance(stride, int)
+            and stride in (1, 2) and isinstance(padding, int) and dilation in (1, (1, 1)))
+
+
+def _adder2d_columns(X, W, stride, padding, dilation):
+    """Every other geometry (5x5, 7x7, rectangular kernels, stride 3, dilation ...): the layer as the
+    reference itself computes it, an explicit im2col around the column-matrix op (adder.py:22-41), with this
+    library's column kernels underneath (`adder`) and autograd's fold as col2im.  Columns are ordered
+    (image, position), which the op does not care about."""
+    n, co = X.shape[0], W.shape[0]
+    cols = torch.nn.functional.unfold(X, (W.shape[2], W.shape[3]), dilation=dilation, padding=padding, stride=stride)
+    k, positions = cols.shape[1], cols.shape[2]
+    Y = adder.apply(W.reshape(co, k), cols.transpose(0, 1).reshape(k, n * positions))
+    pair = lambda v: (v, v) if isinstance(v, int) else tuple(v)
+    (sh, _), (ph, _), (dh, _) = pair(stride), pair(padding), pair(dilation)
+    ho = (X.shape[2] + 2 * ph - dh * (W.shape[2] - 1) - 1) // sh + 1
+    return Y.view(co, n, ho, positions // ho).transpose(0, 1).contiguous()
+
+
+def adder2d_function(X, W, stride=1, padding=0, dilation=1):
+    """Same contract as adder.py:22-41: X[N,Ci,H,W], W[Co,Ci,kh,kw] -> [N,Co,Ho,Wo], differentiable.
+    `dilation` is an extension (the reference fixes it to 1)."""
+    if _fused_geometry(W, stride, padding, dilation):
+        return _Adder2dNCHW.apply(X, W, stride, padding)
+    return _adder2d_columns(X, W, stride, padding, dilation)
 
 
 class adder(Function):
@@ -90,27 +114,30 @@ class adder(Function):
 
 class adder2d(nn.Module):
     """adder.py:83-108.  `depth_wise=True` is rejected: the reference allocates [Co,1,k,k] weights for
-    it but its forward ignores the flag, so no caller can rely on it."""
+    it but its forward ignores the flag, so no caller can rely on it.  3x3 and 1x1 kernels at stride 1 or 2 run
+    on the fused kernels; any other kernel size or stride (and the extensions: a (kh, kw) tuple, `dilation`)
+    runs through the column-matrix kernels behind an explicit im2col."""
 
     def __init__(self, input_channel, output_channel, kernel_size, stride=1, padding=0, bias=False,
-                 depth_wise=False):
+                 depth_wise=False, dilation=1):
         super().__init__()
         if depth_wise:
             raise NotImplementedError("depth_wise adder2d is not implemented (nor computed by the reference)")
         self.stride = stride
         self.padding = padding
+        self.dilation = dilation          # extension: the reference has no dilation (adder.py:32)
         self.input_channel = input_channel
         self.output_channel = output_channel
         self.kernel_size = kernel_size
         self.depth_wise = depth_wise
-        self.adder = torch.nn.Parameter(
-            nn.init.normal_(torch.randn(output_channel, input_channel, kernel_size, kernel_size)))
+        kh, kw = (kernel_size, kernel_size) if isinstance(kernel_size, int) else kernel_size   # (kh, kw): extension
+        self.adder = torch.nn.Parameter(nn.init.normal_(torch.randn(output_channel, input_channel, kh, kw)))
         self.bias = bias
         if bias:
             self.b = torch.nn.Parameter(nn.init.uniform_(torch.zeros(output_channel)))
 
     def forward(self, x):
-        output = adder2d_function(x, self.adder, self.stride, self.padding)
+        output = adder2d_function(x, self.adder, self.stride, self.padding, self.dilation)
         if self.bias:
             output = output + self.b.unsqueeze(0).unsqueeze(2).unsqueeze(3)
         return output
@@ -118,7 +145,7 @@ class adder2d(nn.Module):
     def forward_with_stats(self, x):
         """`(forward(x), st)` where `st` holds the per-channel sums a following batch norm needs
         (`adder_cuda.forward(..., stats=True)`), or None where the layer cannot provide them."""
-        if self.bias or not x.is_cuda:
+        if self.bias or not x.is_cuda or not _fused_geometry(self.adder, self.stride, self.padding, self.dilation):
             return self.forward(x), None
         out, st = _Adder2dNCHW.apply(x, self.adder, self.stride, self.padding, True)
         return out, (st if st.shape[1] > 0 else None)

@@ -240,10 +240,25 @@ struct FwdPlan {
 
 template <int KS, int S, int RW, int RM>
 static int plan_fwd_t(const Geom& g, const float* out, const TileHint& hint, FwdPlan& p) {
+    if (hint.threads == 0) {
+        // 128 threads per CTA unless that leaves the launch with fewer CTAs than two per SM (the deep, small
+        // planes: 64->64 on 8x8 at batch 256 has 256 of them): then 256 threads, i.e. twice the channels per
+        // CTA, so that every staged input patch is used twice as often (60 -> 56 us on that layer) - as long as
+        // that still leaves about one CTA per SM.
+        TileHint h2 = hint;
+        h2.threads = 128;
+        const int st = plan_fwd_t<KS, S, RW, RM>(g, out, h2, p);
+        if (st == ADDER_OK && p.gx * p.gy < 2LL * sm_count() && g.Co > p.a.TM) {
+            FwdPlan q;
+            h2.threads = 256;
+            if (plan_fwd_t<KS, S, RW, RM>(g, out, h2, q) == ADDER_OK && 4 * q.gx * q.gy >= 3LL * sm_count()) p = q;
+        }
+        return st;
+    }
     FwdArgs& a = p.a;
     p.ks = KS; p.s = S; p.rw = RW; p.rm = RM;
     a.g = g;
-    const int threads_target = hint.threads > 0 ? hint.threads : 128;
+    const int threads_target = hint.threads;
     // few channel groups per CTA: the weight slab is re-staged by every CTA, the pixels are not
     const int cg_max = hint.cg > 0 ? hint.cg : (threads_target / 32 > 2 ? threads_target / 32 : 2);
     a.CG = ceil_div(g.Co, RM) < cg_max ? ceil_div(g.Co, RM) : cg_max;

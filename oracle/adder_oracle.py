@@ -206,6 +206,32 @@ REL_TOL = 1e-5
 ABS_TOL = 1e-4
 
 
+def adder2d_general(G, X, W, stride=1, padding=0, dilation=1, eta: float = ETA):
+    """Float64 layer for ANY kernel extent, stride, padding and dilation: (out, grad_x, rescaled grad_w).
+    The same three expressions as the column op (adder.py:58, :70-74, :76-78) on an explicit im2col
+    (adder.py:32-33 generalised by F.unfold's kernel-size / dilation arguments), col2im by F.fold.
+    G may be None (forward only).  Small cases only: materialises [N, Co, K, L]."""
+    F = torch.nn.functional
+    X64, W64 = X.double(), W.double()
+    n, co = X.shape[0], W.shape[0]
+    ksz = (W.shape[2], W.shape[3])
+    cols = F.unfold(X64, ksz, dilation=dilation, padding=padding, stride=stride)           # [N, K, L]
+    D = cols.unsqueeze(1) - W64.reshape(1, co, -1, 1)                                       # x - w, [N, Co, K, L]
+    out_cols = -D.abs().sum(2)                                                              # [N, Co, L]
+    pair = lambda v: (v, v) if isinstance(v, int) else tuple(v)
+    (sh, _), (ph, _), (dh, _) = pair(stride), pair(padding), pair(dilation)
+    ho = (X.shape[2] + 2 * ph - dh * (ksz[0] - 1) - 1) // sh + 1
+    out = out_cols.reshape(n, co, ho, -1)
+    if G is None:
+        return out, None, None
+    g = G.double().reshape(n, co, 1, -1)
+    gw = (D * g).sum((0, 3)).reshape(W.shape)
+    gw = gw / gw.norm(p=2).clamp(min=1e-12) * math.sqrt(W.numel()) * eta
+    gx_cols = ((-D).clamp(-1.0, 1.0) * g).sum(1)                                            # [N, K, L]
+    gx = F.fold(gx_cols, (X.shape[2], X.shape[3]), ksz, dilation=dilation, padding=padding, stride=stride)
+    return out, gx, gw
+
+
 def compare(name: str, got: torch.Tensor, want: torch.Tensor, rel: float = REL_TOL, abs_: float = ABS_TOL):
     """Return (ok, max_abs_err, report) under |got - want| <= abs + rel * |want|."""
     got = got.detach().to("cpu", torch.float64)

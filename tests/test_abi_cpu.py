@@ -90,15 +90,19 @@ def test_module_surface_matches_reference():
     import inspect
     from addernetcuda_b200 import adder
     sig = inspect.signature(adder.adder2d.__init__)
+    # the reference's seven, in its order; `dilation` is an extension appended behind them
     assert list(sig.parameters)[1:] == ["input_channel", "output_channel", "kernel_size", "stride", "padding",
-                                        "bias", "depth_wise"]
+                                        "bias", "depth_wise", "dilation"]
+    assert sig.parameters["dilation"].default == 1
     assert [sig.parameters[p].default for p in ("stride", "padding", "bias", "depth_wise")] == [1, 0, False, False]
     m = adder.adder2d(3, 5, 3, stride=2, padding=1, bias=True)
     assert set(dict(m.named_parameters())) == {"adder", "b"}
     assert tuple(m.adder.shape) == (5, 3, 3, 3) and tuple(m.b.shape) == (5,)
     for attr in ("stride", "padding", "input_channel", "output_channel", "kernel_size", "depth_wise", "bias"):
         assert hasattr(m, attr)
-    assert list(inspect.signature(adder.adder2d_function).parameters) == ["X", "W", "stride", "padding"]
+    assert list(inspect.signature(adder.adder2d_function).parameters) == ["X", "W", "stride", "padding", "dilation"]
+    rect = adder.adder2d(3, 5, (3, 5), padding=(1, 2))
+    assert tuple(rect.adder.shape) == (5, 3, 3, 5)
     assert hasattr(adder.adder, "apply")
     with pytest.raises(NotImplementedError):
         adder.adder2d(4, 4, 3, depth_wise=True)

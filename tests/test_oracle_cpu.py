@@ -88,3 +88,19 @@ def test_resnet20_step_matches_reference_fixture():
     for k, p in grads.items():
         ok, worst, msg = O.compare(k, p.grad, _t(z["grad/" + k]))
         assert ok, msg
+
+
+@pytest.mark.parametrize("stride,padding", [(1, 1), (2, 1), (1, 0)])
+def test_general_geometry_oracle_agrees_with_the_direct_one_on_square_kernels(stride, padding):
+    """adder2d_general (any kernel extent / dilation) restates the same three expressions: on a 3x3 layer
+    it must give what the direct float64 sums give."""
+    torch.manual_seed(5 + stride)
+    x, w = torch.randn(3, 5, 9, 9), torch.randn(7, 5, 3, 3)
+    ho, wo = O.out_hw(9, 9, 3, stride, padding)
+    g = torch.randn(3, 7, ho, wo)
+    out, gx, gw = O.adder2d_general(g, x, w, stride, padding)
+    gx_d, gws_d, _ = O.adder2d_backward_direct(g, x, w, stride, padding)
+    for name, a, b in (("out", out, O.adder2d_forward_direct(x, w, stride, padding)), ("grad_x", gx, gx_d),
+                       ("grad_w", gw, gws_d)):
+        ok, worst, msg = O.compare(name, a, b, 1e-9, 1e-9)
+        assert ok, msg

@@ -79,12 +79,14 @@ def test_special_case_kernels_are_chosen_where_they_apply():
 
 
 def test_chunking_does_not_depend_on_the_batch():
-    """Sub-batches must be computed with the same chunk boundaries (bitwise-equal results per image)."""
-    for op, key in ((0, "CK"), (1, "CKO")):
-        for shape in ((64, 8, 8, 64), (32, 16, 16, 32), (256, 14, 14, 256)):
-            ci, h, w, co = shape
-            values = {_field(_lib.describe_plan(op, n, ci, h, w, co, 3, 1, 1, 1), key) for n in (1, 2, 3, 8, 64, 256)}
-            assert len(values) == 1, (op, shape, values)
+    """Sub-batches must be computed with the same chunk boundaries in the input gradient, whose two-level
+    summation folds one partial sum per chunk (bitwise-equal results per image).  The forward keeps one running
+    sum per output over all input channels, so its bits do not depend on where the chunks are cut; its chunk
+    size may follow the CTA shape, which follows the size of the launch."""
+    for shape in ((64, 8, 8, 64), (32, 16, 16, 32), (256, 14, 14, 256)):
+        ci, h, w, co = shape
+        values = {_field(_lib.describe_plan(1, n, ci, h, w, co, 3, 1, 1, 1), "CKO") for n in (1, 2, 3, 8, 64, 256)}
+        assert len(values) == 1, (shape, values)
 
 
 def test_unsupported_geometry_is_reported_not_planned():
