@@ -6,7 +6,7 @@ import raises.  Nothing here computes on the CPU.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_float, c_int, c_size_t, c_void_p, POINTER
+from ctypes import c_char_p, c_float, c_int, c_longlong, c_size_t, c_uint, c_ulonglong, c_void_p, POINTER
 from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
@@ -16,6 +16,9 @@ TUNING_LIB_PATH = _PKG / "libadder_b200_tuning.so"
 ADDER_OK = 0
 FLAG_FAST_CLAMP = 1
 FLAG_ACCUMULATE = 2
+# status codes of include/adder_b200.h
+(OK, ERR_NULL_POINTER, ERR_BAD_SHAPE, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_WORKSPACE, ERR_CUDA, ERR_INTERNAL,
+ ERR_TOO_LARGE, ERR_TIMEOUT) = range(10)
 
 _GEOM = [c_int] * 8  # n, ci, h, w, co, k, stride, pad
 
@@ -53,6 +56,15 @@ SIGNATURES = {
                                               c_void_p]),
     "adder_b200_affine_forward": (c_int, [c_void_p] * 5 + [c_int, c_int, c_int, c_int, c_void_p]),
     "adder_b200_device_status": (c_int, [POINTER(c_int), c_int]),
+    "adder_b200_peer_area_bytes": (c_size_t, [c_longlong, c_int]),
+    "adder_b200_ipc_export": (c_int, [c_void_p, c_void_p, POINTER(c_ulonglong)]),
+    "adder_b200_ipc_open": (c_int, [c_void_p, c_ulonglong, POINTER(c_void_p)]),
+    "adder_b200_ipc_close": (c_int, [c_void_p, c_ulonglong]),
+    "adder_b200_peer_comm_create": (c_int, [POINTER(c_void_p), c_int, c_int, c_int, c_void_p, c_void_p, c_longlong,
+                                            c_int, c_int]),
+    "adder_b200_peer_allreduce": (c_int, [c_void_p, c_void_p]),
+    "adder_b200_peer_comm_status": (c_int, [c_void_p, POINTER(c_int), POINTER(c_uint), c_int]),
+    "adder_b200_peer_comm_destroy": (c_int, [c_void_p]),
     "adder_b200_describe_plan": (c_int, [c_int, *_GEOM, c_int, c_char_p, c_size_t]),
 }
 # exported by libadder_b200_tuning.so only (the header's ADDER_B200_TUNING section)

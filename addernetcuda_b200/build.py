@@ -22,7 +22,7 @@ CSRC = PKG / "csrc"
 INCLUDE = PKG.parent / "include"
 LIB = PKG / "libadder_b200.so"
 TUNING_LIB = PKG / "libadder_b200_tuning.so"   # same objects, api.cu compiled with -DADDER_B200_TUNING
-SOURCES = ["api.cu", "adder_fwd.cu", "adder_bwd_input.cu", "adder_bwd_weight.cu", "adder_bwd_weight_pipe.cu", "adder_bwd_weight_tma.cu", "tma_host.cu", "adder_bwd_weight_1x1.cu", "adder_pointwise.cu", "static_scratch.cu", "batchnorm.cu"]
+SOURCES = ["api.cu", "adder_fwd.cu", "adder_bwd_input.cu", "adder_bwd_weight.cu", "adder_bwd_weight_pipe.cu", "adder_bwd_weight_tma.cu", "tma_host.cu", "adder_bwd_weight_1x1.cu", "adder_pointwise.cu", "static_scratch.cu", "batchnorm.cu", "peer_allreduce.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

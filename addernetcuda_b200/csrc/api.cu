@@ -106,6 +106,7 @@ const char* adder_b200_status_string(int status) {
         case ADDER_ERR_CUDA: return "CUDA runtime error";
         case ADDER_ERR_INTERNAL: return "internal tile-planning error";
         case ADDER_ERR_TOO_LARGE: return "layer needs more scratch than the fixed in-library array holds";
+        case ADDER_ERR_TIMEOUT: return "a bounded device-side wait ran out (a peer rank never arrived)";
         default: return "unknown status";
     }
 }

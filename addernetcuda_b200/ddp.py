@@ -13,7 +13,10 @@ Mechanics
     are packed into the flat buffer with one multi-tensor copy, `.grad` is re-pointed at the views,
     and the all-reduce is enqueued on a side stream that waits for the packing only;
   * the reduction averages (NCCL's AVG operator), so no scaling pass follows it; `finish()` only makes
-    the compute stream wait for the side stream (with gloo, which can only sum, it also scales).
+    the compute stream wait for the side stream (with gloo, which can only sum, it also scales);
+  * on one node with NVLink peers, buckets of up to 8 MB skip NCCL: one kernel of this library pushes the
+    bucket into a receive area on every rank, waits (bounded) for the others' pushes and adds them in rank
+    order (`peer.PeerAllReduce`) - one launch and one NVLink round per bucket instead of a ring.
 Everything is stream-ordered (no host synchronisation), so a whole training step, collectives
 included, can be captured in a CUDA graph.  Works on CPU tensors with the gloo backend (tests).
 """
@@ -29,7 +32,8 @@ class _Bucket:
     def __init__(self, params: List[torch.nn.Parameter], device, dtype):
         self.params = params
         self.numel = sum(p.numel() for p in params)
-        self.flat = torch.zeros(self.numel, device=device, dtype=dtype)
+        # padded to whole 128-bit words (the peer all-reduce moves quads); the pad stays zero
+        self.flat = torch.zeros((self.numel + 3) // 4 * 4, device=device, dtype=dtype)
         self.views = []
         off = 0
         for p in params:
@@ -37,6 +41,7 @@ class _Bucket:
             off += p.numel()
         self.pending = len(params)
         self.work = None
+        self.peer = None          # peer.PeerAllReduce when the bucket is exchanged over peer memory
 
 
 class BucketedDDP:
@@ -52,7 +57,7 @@ class BucketedDDP:
     """
 
     def __init__(self, module: torch.nn.Module, bucket_mb: Optional[float] = None, process_group=None,
-                 broadcast_from_rank0: bool = True):
+                 broadcast_from_rank0: bool = True, peer_reduce: Optional[bool] = None, peer_max_polls: Optional[int] = None):
         if not dist.is_initialized():
             raise RuntimeError("torch.distributed must be initialised before BucketedDDP")
         self.module = module
@@ -97,6 +102,49 @@ class BucketedDDP:
         # NCCL averages inside the reduction; gloo only sums, so its buckets are scaled in finish()
         self._avg_in_reduce = self.is_cuda and dist.get_backend(process_group) == "nccl"
         self.launch_order: List[int] = []   # bucket indices in the order their all-reduce was enqueued
+        # peer_reduce: None = use the one-kernel exchange where it applies, False = NCCL only, True = require it
+        self.peer_arena = None
+        if peer_reduce is not False and self.world > 1:
+            self._setup_peer_reduce(required=bool(peer_reduce), max_polls=peer_max_polls)
+
+    def _setup_peer_reduce(self, required: bool, max_polls: Optional[int]) -> None:
+        """All ranks decide together: either every eligible bucket goes over peer memory on every rank, or none."""
+        from . import peer
+        eligible = [b for b in self.buckets
+                    if b.flat.dtype == torch.float32 and b.flat.numel() * 4 <= peer.MAX_BUCKET_BYTES]
+        ok = self._avg_in_reduce and bool(eligible)
+        err: Optional[Exception] = None
+        if ok:
+            ok = peer.same_host(self.group)
+        if ok:
+            try:
+                sizes = [peer.PeerAllReduce.area_bytes(b.flat.numel(), self.world) for b in eligible]
+                self.peer_arena = peer.PeerArena(sum(sizes), self.device, self.group)
+            except Exception as e:          # no IPC / no peer access on this machine
+                ok, err = False, e
+        flag = torch.tensor([1 if ok else 0], device=self.device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 0:
+            self.peer_arena = None
+            if required:
+                raise RuntimeError(f"peer_reduce=True but the peer-memory exchange cannot be set up here: {err}")
+            return
+        off = 0
+        kw = {} if max_polls is None else {"max_polls": int(max_polls)}
+        for b, sz in zip(eligible, sizes):
+            b.peer = peer.PeerAllReduce(b.flat, self.peer_arena, off, **kw)
+            off += sz
+        dist.barrier(group=self.group)
+
+    def check(self) -> None:
+        """Raises if a peer exchange gave up waiting for another rank (synchronises the device).  Call it
+        where a host synchronisation is acceptable: after a validation pass, every so many steps, at the end."""
+        for i, b in enumerate(self.buckets):
+            if b.peer is not None:
+                st = b.peer.status(reset=True)
+                if st != 0:
+                    raise RuntimeError(f"BucketedDDP: the peer exchange of bucket {i} timed out waiting for another "
+                                       f"rank (status {st}); its gradients were not averaged")
 
     # ------------------------------------------------------------------ hooks
     def _on_grad(self, p: torch.nn.Parameter) -> None:
@@ -125,8 +173,11 @@ class BucketedDDP:
         if self.is_cuda:
             self.comm_stream.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(self.comm_stream):
-                dist.all_reduce(b.flat, op=dist.ReduceOp.AVG if self._avg_in_reduce else dist.ReduceOp.SUM,
-                                group=self.group)
+                if b.peer is not None:
+                    b.peer.launch(self.comm_stream)
+                else:
+                    dist.all_reduce(b.flat, op=dist.ReduceOp.AVG if self._avg_in_reduce else dist.ReduceOp.SUM,
+                                    group=self.group)
         else:
             b.work = dist.all_reduce(b.flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
 

@@ -407,7 +407,8 @@ def run_gpu_arm(args):
     net = net.to(dev).train()
     if args.sync_bn and world > 1:
         net = torch.nn.SyncBatchNorm.convert_sync_batchnorm(net)
-    ddp = BucketedDDP(net, bucket_mb=args.bucket_mb) if world > 1 else None
+    peer_reduce = {"auto": None, "on": True, "off": False}[args.exchange]
+    ddp = BucketedDDP(net, bucket_mb=args.bucket_mb, peer_reduce=peer_reduce) if world > 1 else None
     ts = TrainStep(net, shape, classes, lr=0.1, momentum=0.9, ddp=ddp, use_graph=not args.no_graph, device=dev)
 
     import numpy as np
@@ -433,6 +434,8 @@ def run_gpu_arm(args):
     for _ in range(W):
         ts.run()
     barrier()
+    if ddp is not None:
+        ddp.check()      # a peer exchange that gave up waiting must not be timed as if it had worked
 
     # ---- value: K steps, batch resident in device memory
     sampler = ClockSampler(local_rank)
@@ -463,6 +466,8 @@ def run_gpu_arm(args):
     e1.record()
     barrier()
     ms_e2e = max_over_ranks(e0.elapsed_time(e1))
+    if ddp is not None:
+        ddp.check()
     h2d = host_images.numel() * 4 + host_labels.numel() * 8
     d2h = 4
 
@@ -491,6 +496,9 @@ def run_gpu_arm(args):
                        "input_grad_clamp": "exact" if args.exact_clamp else "saturating-add form",
                        "batchnorm": "sync" if (args.sync_bn and world > 1) else "per-rank",
                        "parallelism": f"dp{world}", "buckets": len(ddp.buckets) if ddp is not None else 0,
+                       "exchange": ("none" if ddp is None else
+                                    "one-kernel push/wait/add over peer memory" if all(b.peer is not None for b in ddp.buckets)
+                                    else "nccl all-reduce" if all(b.peer is None for b in ddp.buckets) else "mixed"),
                        "l2": "not flushed between steps: one step streams far more than the 126 MB L2"},
             "e2e": {"value": world * B * K / (ms_e2e * 1e-3), "unit": "images/s", "ms_per_step": ms_e2e / K,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -634,6 +642,9 @@ def main():
                     help="gradient bucket size; default: a third of the model's gradients, at most 25 MB")
     ap.add_argument("--sync-bn", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--exchange", choices=["auto", "on", "off"], default="auto",
+                    help="gradient exchange at N > 1: this library's peer-memory kernel where it applies (auto), "
+                         "required (on), or NCCL only (off)")
     ap.add_argument("--exact-clamp", action="store_true", help="input gradient with min/max instead of the saturating add")
     ap.add_argument("--skip-layers", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true")

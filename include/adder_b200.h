@@ -46,7 +46,8 @@ enum {
     ADDER_ERR_WORKSPACE = 5,     /* workspace missing or smaller than the *_workspace_bytes() answer */
     ADDER_ERR_CUDA = 6,          /* the CUDA runtime rejected a launch or an attribute */
     ADDER_ERR_INTERNAL = 7,      /* tile planner produced an impossible plan (a bug) */
-    ADDER_ERR_TOO_LARGE = 8      /* the layer needs more scratch than a fixed-capacity entry point owns */
+    ADDER_ERR_TOO_LARGE = 8,     /* the layer needs more scratch than a fixed-capacity entry point owns */
+    ADDER_ERR_TIMEOUT = 9        /* a bounded device-side wait ran out (a peer rank never arrived) */
 };
 
 /* flags for the backward entry points */
@@ -200,6 +201,34 @@ ADDER_API int adder_b200_affine_forward(const float* y, const float* scale, cons
  * current device into *status (0 = never happened) and, with reset != 0, clears it.  Synchronises with
  * the device.  No reference counterpart. */
 ADDER_API int adder_b200_device_status(int* status, int reset);
+
+/* ---- gradient exchange between the GPUs of one node (batch-sharded training) ---------------------
+ * The reference trains on one GPU (nn.DataParallel appears only in its evaluation script, test.py:37); with
+ * one process per GPU the per-rank gradients (adder weight gradients already rescaled, adder.py:78) have to
+ * be averaged once per step.  adder_b200_peer_allreduce does that for one flat fp32 bucket in ONE kernel
+ * over peer memory: every rank stores its bucket into a receive area of every rank, signals per chunk, waits
+ * (bounded) for the other ranks' chunks and adds them in rank order - bit-identical results on all ranks.
+ *
+ * Set-up, once per bucket: each rank allocates a zeroed, 16-byte aligned receive area of
+ * adder_b200_peer_area_bytes(n, world) bytes in ordinary device memory, exports it with
+ * adder_b200_ipc_export (handle + offset of the pointer inside its allocation), the ranks exchange those 72
+ * bytes by any means, map each other's areas with adder_b200_ipc_open (once per distinct handle per process)
+ * and synchronise once; then adder_b200_peer_comm_create(areas = the world area pointers as seen from this
+ * process, own area included; n % 4 == 0; chunks = 0 lets the library choose; max_polls bounds the wait, a
+ * poll being 32-256 ns).  first_rank / ranks_here / data[ranks_here] describe the ranks this process drives:
+ * one in production; several only to emulate a multi-rank exchange on one GPU (a single cooperative launch).
+ * The call is stream-ordered and can be captured in a CUDA graph (the epoch counter lives in device memory).
+ * A wait that ran out leaves ADDER_ERR_TIMEOUT in the communicator's status word: read it with
+ * adder_b200_peer_comm_status (a device-to-host copy; reset != 0 clears it). */
+ADDER_API size_t adder_b200_peer_area_bytes(long long n, int world);
+ADDER_API int adder_b200_ipc_export(const void* ptr, unsigned char* handle64, unsigned long long* offset);
+ADDER_API int adder_b200_ipc_open(const unsigned char* handle64, unsigned long long offset, void** ptr);
+ADDER_API int adder_b200_ipc_close(void* ptr, unsigned long long offset);
+ADDER_API int adder_b200_peer_comm_create(void** comm, int world, int first_rank, int ranks_here, float* const* data,
+                                          void* const* areas, long long n, int chunks, int max_polls);
+ADDER_API int adder_b200_peer_allreduce(void* comm, void* stream);
+ADDER_API int adder_b200_peer_comm_status(void* comm, int* status, unsigned* epoch, int reset);
+ADDER_API int adder_b200_peer_comm_destroy(void* comm);
 
 #ifdef ADDER_B200_TUNING
 /* ---- tuning build only (libadder_b200_tuning.so, compiled with -DADDER_B200_TUNING) ---------------

@@ -20,7 +20,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, peer):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -53,12 +53,16 @@ def _worker(rank, world, port, q):
             want[k] = t / world
         # bucketed, overlapped reduction; the bucket size comes from the model: three or more buckets
         net = build()
-        ddp = BucketedDDP(net)
+        ddp = BucketedDDP(net, peer_reduce=peer)
         assert len(ddp.buckets) >= 3, len(ddp.buckets)
+        # peer=True: every bucket is exchanged by this library's one-kernel push/wait/add over peer memory;
+        # peer=False: NCCL's all-reduce
+        assert all((b.peer is not None) == peer for b in ddp.buckets)
         ddp.zero_grad()
         torch.nn.functional.cross_entropy(net(images), labels).backward()
         ddp.finish()
         torch.cuda.synchronize()
+        ddp.check()
         for k, p in net.named_parameters():
             err = (p.grad - want[k]).abs().max().item()
             assert err <= 1e-6 + 1e-5 * want[k].abs().max().item(), f"{k}: {err}"
@@ -104,21 +108,27 @@ def _worker(rank, world, port, q):
         gathered = [torch.empty_like(w) for _ in range(world)]
         dist.all_gather(gathered, w)
         assert torch.equal(gathered[0], gathered[1]), "replicas diverged"
+        ddp.check()
+        print(f"rank {rank}: 6 graph-captured steps, exchange by {'peer-memory kernel' if peer else 'NCCL'}, "
+              f"losses {losses[0]:.4f} -> {losses[-1]:.4f}, replicas identical", flush=True)
         q.put((rank, "ok"))
     except Exception as e:  # pragma: no cover
         import traceback
         q.put((rank, "".join(traceback.format_exception(e))))
     finally:
         torch.cuda.synchronize()
+        q.close()
+        q.join_thread()  # the result must have left the feeder thread before the hard exit below
         os._exit(0)      # leave without communicator teardown (live CUDA graphs hold captured collectives)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_gpu_bucketed_allreduce_and_graph_step():
+@pytest.mark.parametrize("peer", [False, True], ids=["nccl", "peer_memory"])
+def test_two_gpu_bucketed_allreduce_and_graph_step(peer):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, peer)) for r in range(2)]
     for p in procs:
         p.start()
     results = [q.get(timeout=240) for _ in procs]
