@@ -39,11 +39,14 @@ class _Adder2dNCHW(Function):
         if want_stats:
             out, st = adder_cuda.forward(x, w, stride, padding, stats=True)
             ctx.mark_non_differentiable(st)
+            ctx.set_materialize_grads(False)     # no zero-filled "gradient" of the statistics in backward
             return out, st
         return adder_cuda.forward(x, w, stride, padding)
 
     @staticmethod
     def backward(ctx, grad_out, *_unused):
+        if grad_out is None:
+            return None, None, None, None, None
         x, w = ctx.saved_tensors
         grad_out = grad_out.contiguous()
         gx = gw = None
