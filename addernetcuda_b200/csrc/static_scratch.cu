@@ -60,12 +60,9 @@ int adder_b200_backward_weight_static(const float* grad_out, const float* x, con
     if (n > 0 && (grad_out == nullptr || x == nullptr)) return ADDER_ERR_NULL_POINTER;
     // Same geometry rules and the same scratch requirement as the workspace-taking entry point.
     const size_t need = adder_b200_backward_weight_workspace_bytes(n, ci, h, wd, co, k, stride, pad);
-    if (need == 0) {
-        int ho = 0, wo = 0;
-        const int st = adder_b200_output_size(h, wd, k, stride, pad, &ho, &wo);
-        if (st != ADDER_OK) return st;
-        return (n < 0 || ci <= 0 || co <= 0) ? ADDER_ERR_BAD_SHAPE : ADDER_ERR_UNSUPPORTED;
-    }
+    if (need == 0)   // invalid geometry or no plan: the workspace-taking entry point reports which (it cannot launch without scratch)
+        return adder_b200_backward_weight(grad_out, x, w, grad_w, eta, out_norm, nullptr, 0, n, ci, h, wd, co, k, stride,
+                                          pad, 0, stream);
     if (need > kScratchBytes) return ADDER_ERR_TOO_LARGE;
     void* scratch = nullptr;
     const int st = scratch_address(&scratch);

@@ -135,6 +135,29 @@ class BucketedDDP:
             b.peer = peer.PeerAllReduce(b.flat, self.peer_arena, off, **kw)
             off += sz
         dist.barrier(group=self.group)
+        # Self-test before the first real step: every bucket is exchanged once by the kernel and once by NCCL on
+        # rank-dependent values; unless both agree on every rank, all ranks go back to NCCL together.
+        good = True
+        rank = dist.get_rank(self.group)
+        with torch.no_grad():
+            for b in eligible:
+                probe = torch.arange(b.flat.numel(), device=self.device, dtype=torch.float32).remainder_(251.0)
+                probe = probe * (0.25 + 0.5 * rank) + rank
+                want = probe.clone()
+                dist.all_reduce(want, op=dist.ReduceOp.SUM, group=self.group)
+                want /= self.world
+                b.flat.copy_(probe)
+                b.peer.launch()
+                torch.cuda.synchronize(self.device)
+                good = good and b.peer.status(reset=True) == 0 and bool(torch.allclose(b.flat, want, rtol=1e-6, atol=1e-6))
+                b.flat.zero_()
+        flag = torch.tensor([1 if good else 0], device=self.device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 0:
+            for b in eligible:
+                b.peer = None
+            if required:
+                raise RuntimeError("peer_reduce=True but the peer-memory exchange failed its self-test against NCCL")
 
     def check(self) -> None:
         """Raises if a peer exchange gave up waiting for another rank (synchronises the device).  Call it

@@ -109,8 +109,11 @@ ADDER_API int adder_b200_backward_weight(const float* grad_out, const float* x, 
  * A layer whose partial sums need more returns ADDER_ERR_TOO_LARGE: use the workspace-taking entry
  * point for it.  All calls on a device share that array, so calls that can overlap on the GPU
  * (different streams without a dependency) race: serialise them.  Nothing in the array needs
- * clearing between calls.  The first call on each device looks up the array's device address; make
- * it outside any stream capture.  Results are identical to adder_b200_backward_weight().
+ * clearing between calls.  The first call on each device looks up the array's device address, and with
+ * CUDA's lazy module loading that look-up is also the moment the driver loads this part of the library and
+ * reserves the array's 8 MiB: make one warm-up call per device (n = 0 is enough) at plug-in initialisation,
+ * before the host's memory manager claims the GPU and outside any stream capture; later calls then truly
+ * allocate nothing.  Results are identical to adder_b200_backward_weight().
  * This entry point has no counterpart in the reference. */
 #define ADDER_B200_STATIC_SCRATCH_BYTES (8u << 20)
 ADDER_API size_t adder_b200_static_scratch_bytes(void);
