@@ -196,7 +196,7 @@ __global__ void __launch_bounds__(256, MB) adder_gx_kernel(const GxArgs a) {
         for (int j = 0; j < RW; ++j) {
             const int wi = (q0 + j) * S + pw;
             const bool ok = active && n < a.g.N && ci < a.g.Ci && hi < a.g.H && wi < a.g.W;
-            const float v = ok ? __ldg(a.x + ((size_t)(n * a.g.Ci + ci) * HW + hi * a.g.W + wi)) : 0.f;
+            const float v = ok ? __ldg(a.x + ((size_t)(n * a.g.Ci + ci) * a.x_plane + hi * a.x_row + wi * a.samp)) : 0.f;
             xv[c][j] = FAST ? -0.5f * v : v;
             acc[c][j] = 0.f;
         }
@@ -392,6 +392,28 @@ __global__ void __launch_bounds__(256, MB) adder_gx_kernel(const GxArgs a) {
                     v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
                 }
                 *o4 = v;
+            }
+            continue;
+        }
+        if (KS == 1 && S == 1 && a.samp > 1) {
+            // sampled grid: pixel (hi, wi) of the grid is pixel (hi*samp, wi*samp) of the real tensor; the other
+            // pixels of its samp x samp block are read by no output and get zero (left alone when accumulating)
+            float* ob = a.gx + ((size_t)(n * a.g.Ci + ci) * a.x_plane + (size_t)hi * a.x_row);
+#pragma unroll
+            for (int j = 0; j < RW; ++j) {
+                const int wi = q0 + j;
+                if (wi >= a.g.W) break;
+                const float v = FAST ? 2.f * acc[c][j] - box[j] : acc[c][j];
+                float* px = ob + wi * a.samp;
+                if (a.accumulate) { *px += v; continue; }
+                if (a.samp_pairs) {
+                    *reinterpret_cast<float2*>(px) = make_float2(v, 0.f);
+                    if (hi * 2 + 1 < a.real_h) *reinterpret_cast<float2*>(px + a.real_w) = make_float2(0.f, 0.f);
+                } else {
+                    for (int dr = 0; dr < a.samp && hi * a.samp + dr < a.real_h; ++dr)
+                        for (int dc = 0; dc < a.samp && wi * a.samp + dc < a.real_w; ++dc)
+                            px[dr * a.real_w + dc] = (dr | dc) ? 0.f : v;
+                }
             }
             continue;
         }
@@ -750,14 +772,26 @@ static int plan_gx_t(const Geom& g, const TileHint& hint, GxPlan& p) {
     return plan_gx_n<KS, S, RW, RC, FAST>(g, hint, p, 1);
 }
 
+// The geometry the kernels tile: the layer itself, or - for a strided, unpadded 1x1 layer - the stride-1 layer on
+// the grid of sampled pixels (every unsampled input pixel has a zero gradient and is not worth a thread).
+static Geom gx_tiling_geom(const Geom& g) {
+    Geom t = g;
+    if (g.k == 1 && g.stride > 1 && g.pad == 0) { t.H = g.Ho; t.W = g.Wo; t.stride = 1; }
+    return t;
+}
+
 template <int KS, int S, int RW, int RC, bool FAST>
-static int launch_gx_t(const Geom& g, const float* gout, const float* x, const float* w, float* gx,
+static int launch_gx_t(const Geom& real, const float* gout, const float* x, const float* w, float* gx,
                        int accumulate, const TileHint& hint, cudaStream_t stream) {
     GxPlan p;
+    const Geom g = gx_tiling_geom(real);
     const int st = plan_gx_t<KS, S, RW, RC, FAST>(g, hint, p);
     if (st != ADDER_OK) return st;
     p.a.gout = gout; p.a.x = x; p.a.w = w; p.a.gx = gx; p.a.accumulate = accumulate;
-    p.a.vec_io = (S == 1 && RW % 4 == 0 && g.W % 4 == 0 &&
+    p.a.samp = (KS == 1 && S == 1) ? real.stride : 1;
+    p.a.x_plane = real.H * real.W; p.a.x_row = real.W * p.a.samp; p.a.real_h = real.H; p.a.real_w = real.W;
+    p.a.samp_pairs = (p.a.samp == 2 && real.W % 2 == 0 && (reinterpret_cast<uintptr_t>(gx) & 7) == 0) ? 1 : 0;
+    p.a.vec_io = (S == 1 && RW % 4 == 0 && g.W % 4 == 0 && p.a.samp == 1 &&
                   ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(gx)) & 15) == 0) ? 1 : 0;
     if constexpr (KS == 3 && S == 2 && RW <= 4) {
         if (p.a.nseg == 2) {
@@ -788,13 +822,15 @@ static int choose_gx_rw(const Geom& g, const TileHint& hint) {
     const int class_px = ceil_div(g.W, g.stride);
     if ((class_px % 8 != 0) && (class_px % 7 == 0)) return 7;
     if (class_px % 4 != 0) return 8;
-    return 4;      // 4-pixel segments won every sweep of the ResNet-20 layer shapes
+    if (g.k == 1 && class_px % 8 == 0) return 8;     // one tap per channel: the wider tile halves the loads per term
+    return 4;      // 4-pixel segments won every sweep of the 3x3 ResNet-20 layer shapes
 }
 
 #define ADDER_GX_DISPATCH(CALL)                                                             \
     if (g.k == 3 && g.stride == 1) { ADDER_GX_TILES(3, 1, CALL) }                           \
     else if (g.k == 3 && g.stride == 2) { ADDER_GX_TILES(3, 2, CALL) }                      \
     else if (g.k == 1 && g.stride == 1) { ADDER_GX_TILES(1, 1, CALL) }                      \
+    else if (g.k == 1 && g.stride == 2 && g.pad == 0) { ADDER_GX_TILES(1, 1, CALL) }          \
     else if (g.k == 1 && g.stride == 2) { ADDER_GX_TILES(1, 2, CALL) }
 #define ADDER_GX_TILES(KS_, S_, CALL)                                                       \
     if (rw == 7) { if (fast) { CALL(KS_, S_, 7, 4, true) } else { CALL(KS_, S_, 7, 4, false) } }        \
@@ -807,10 +843,11 @@ int describe_gx(const Geom& g, int fast, const TileHint& hint, char* buf, size_t
                  "grid=(%d,%d) status=0", g.stride, fast, ceil_div(g.N * g.Ho * g.Wo, 256), ceil_div(g.Ci, 16));
         return ADDER_OK;
     }
-    const int rw = choose_gx_rw(g, hint);
+    const Geom tg = gx_tiling_geom(g);
+    const int rw = choose_gx_rw(tg, hint);
     GxPlan p;
     int st = ADDER_ERR_UNSUPPORTED;
-#define ADDER_GX_PLAN(KS_, S_, RW_, RC_, FAST_) st = plan_gx_t<KS_, S_, RW_, RC_, FAST_>(g, hint, p);
+#define ADDER_GX_PLAN(KS_, S_, RW_, RC_, FAST_) st = plan_gx_t<KS_, S_, RW_, RC_, FAST_>(tg, hint, p);
     ADDER_GX_DISPATCH(ADDER_GX_PLAN)
 #undef ADDER_GX_PLAN
     if (st == ADDER_ERR_UNSUPPORTED && !((g.k == 1 || g.k == 3) && (g.stride == 1 || g.stride == 2))) return st;
@@ -825,7 +862,7 @@ int describe_gx(const Geom& g, int fast, const TileHint& hint, char* buf, size_t
 int launch_gx(const Geom& g, const float* gout, const float* x, const float* w, float* gx, int fast,
               int accumulate, const TileHint& hint, cudaStream_t stream) {
     if (hint.is_default() && pointwise_applicable(g)) return launch_pointwise_gx(g, gout, x, w, gx, fast, accumulate, stream);
-    const int rw = choose_gx_rw(g, hint);
+    const int rw = choose_gx_rw(gx_tiling_geom(g), hint);
 #define ADDER_GX_LAUNCH(KS_, S_, RW_, RC_, FAST_) \
     return launch_gx_t<KS_, S_, RW_, RC_, FAST_>(g, gout, x, w, gx, accumulate, hint, stream);
     ADDER_GX_DISPATCH(ADDER_GX_LAUNCH)

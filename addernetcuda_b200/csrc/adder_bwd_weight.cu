@@ -465,7 +465,7 @@ static GwPlan plan_gw(const Geom& g, const TileHint& hint) {
             p.a.splits = sp;
         }
     }
-    if (p.status == ADDER_OK && gw1x1_applicable(g) && hint.rm != 9) {
+    if (p.status == ADDER_OK && gw1x1_applicable(g) && hint.variant == 0) {     // variant 1 asks for the tiled kernel
         p.use_1x1 = true;
         p.a.splits = gw1x1_splits(g);
     }

@@ -1,5 +1,7 @@
-// Weight gradient of a 1x1, stride-1 adder layer as an fp32 SIMT "NT GEMM":
-//   sum_xg[co][ci] = sum_{n,p} g[n][co][p] * x[n][ci][p]        (p runs over the H*W pixels of an image)
+// Weight gradient of a 1x1, unpadded adder layer as an fp32 SIMT "NT GEMM":
+//   sum_xg[co][ci] = sum_{n,p} g[n][co][p] * x[n][ci][p]        (p runs over the Ho*Wo output pixels of an image)
+// For a strided layer x[n][ci][p] is the sampled pixel (stride*(p / Wo), stride*(p % Wo)) of the input plane:
+// the x tile is then gathered with 4-byte copies, everything else is unchanged (GATHER).
 // Both operands are contiguous along p, so tiles [rows][32 pixels] are staged with 16-byte cp.async
 // (4-byte when H*W is not a multiple of 4) and read back with 128-bit loads, four pixels at a time.
 // CTA = 128 threads, output tile 128 co x 64 ci, thread tile 8 x 8 (rows interleaved by 16 / 8 so that
@@ -22,9 +24,11 @@ struct Gw1x1Args {
     float* gsum_part;    // [splits][Co]
     unsigned int* ticket;
     int N, Co, Ci, HW, splits, stages_per_split, total_stages, chunks, n_ci_tiles;
+    int x_plane, x_w, samp;   // GATHER: pixels of an input plane, its row length, sampling stride
+    FastDiv d_wo;             // GATHER: divides a pixel index by Wo
 };
 
-template <bool VEC>
+template <bool VEC, bool GATHER = false>
 __global__ void __launch_bounds__(G1_THREADS, 3) adder_gw1x1_kernel(const Gw1x1Args a) {
     extern __shared__ __align__(16) float smem[];
     constexpr int G_STAGE = G1_TM * G1_PITCH, X_STAGE = G1_TN * G1_PITCH;
@@ -62,11 +66,22 @@ __global__ void __launch_bounds__(G1_THREADS, 3) adder_gw1x1_kernel(const Gw1x1A
                 const float* src = ok ? a.g + ((size_t)n * a.Co + co0 + r) * a.HW + k0 + q : a.g;
                 cp_async16(gd + r * G1_PITCH + q, src, ok);
             }
+            if (GATHER) {
+                for (int e = tid; e < G1_TN * G1_KC; e += G1_THREADS) {
+                    const int r = e >> 5, q = e & 31;
+                    const bool ok = (ci0 + r < a.Ci) && (k0 + q < a.HW);
+                    uint32_t ho, wo;
+                    a.d_wo.divmod(ok ? k0 + q : 0, ho, wo);
+                    const float* src = a.x + ((size_t)n * a.Ci + (ok ? ci0 + r : 0)) * a.x_plane + (size_t)ho * a.samp * a.x_w + wo * a.samp;
+                    cp_async4(xd + r * G1_PITCH + q, ok ? src : a.x, ok);
+                }
+            } else {
             for (int e = tid; e < G1_TN * (G1_KC / 4); e += G1_THREADS) {
                 const int r = e >> 3, q = (e & 7) * 4;
                 const bool ok = (ci0 + r < a.Ci) && (k0 + q < a.HW);
                 const float* src = ok ? a.x + ((size_t)n * a.Ci + ci0 + r) * a.HW + k0 + q : a.x;
                 cp_async16(xd + r * G1_PITCH + q, src, ok);
+            }
             }
         } else {
             for (int e = tid; e < G1_TM * G1_KC; e += G1_THREADS) {
@@ -78,7 +93,14 @@ __global__ void __launch_bounds__(G1_THREADS, 3) adder_gw1x1_kernel(const Gw1x1A
             for (int e = tid; e < G1_TN * G1_KC; e += G1_THREADS) {
                 const int r = e >> 5, q = e & 31;
                 const bool ok = (ci0 + r < a.Ci) && (k0 + q < a.HW);
-                const float* src = ok ? a.x + ((size_t)n * a.Ci + ci0 + r) * a.HW + k0 + q : a.x;
+                const float* src = a.x;
+                if (GATHER) {
+                    uint32_t ho, wo;
+                    a.d_wo.divmod(ok ? k0 + q : 0, ho, wo);
+                    if (ok) src = a.x + ((size_t)n * a.Ci + ci0 + r) * a.x_plane + (size_t)ho * a.samp * a.x_w + wo * a.samp;
+                } else if (ok) {
+                    src = a.x + ((size_t)n * a.Ci + ci0 + r) * a.HW + k0 + q;
+                }
                 cp_async4(xd + r * G1_PITCH + q, src, ok);
             }
         }
@@ -139,13 +161,13 @@ __global__ void __launch_bounds__(G1_THREADS, 3) adder_gw1x1_kernel(const Gw1x1A
 }
 
 bool gw1x1_applicable(const Geom& g) {
-    return g.k == 1 && g.stride == 1 && g.pad == 0 && g.Co >= 64 && g.Ci >= 32 && g.N >= 1;
+    return g.k == 1 && g.pad == 0 && g.Co >= 64 && g.Ci >= 32 && g.N >= 1;     // any stride: strided layers gather x
 }
 
 // Number of batch slices (CTAs per output tile): about three CTAs per SM in total.
 int gw1x1_splits(const Geom& g) {
     const int out_tiles = ceil_div(g.Co, G1_TM) * ceil_div(g.Ci, G1_TN);
-    const int total = g.N * ceil_div(g.H * g.W, G1_KC);
+    const int total = g.N * ceil_div(g.Ho * g.Wo, G1_KC);
     int splits = ceil_div(3 * sm_count(), out_tiles);
     if (splits > total) splits = total;
     if (splits < 1) splits = 1;
@@ -157,7 +179,9 @@ int launch_gw1x1(const Geom& g, const float* gout, const float* x, float* part, 
                  unsigned int* ticket, int splits, cudaStream_t stream) {
     Gw1x1Args a;
     a.g = gout; a.x = x; a.part = part; a.gsum_part = gsum_part; a.ticket = ticket;
-    a.N = g.N; a.Co = g.Co; a.Ci = g.Ci; a.HW = g.H * g.W;
+    a.N = g.N; a.Co = g.Co; a.Ci = g.Ci; a.HW = g.Ho * g.Wo;
+    a.x_plane = g.H * g.W; a.x_w = g.W; a.samp = g.stride; a.d_wo = FastDiv((uint32_t)g.Wo);
+    const bool gather = g.stride != 1;
     a.splits = splits;
     a.chunks = ceil_div(a.HW, G1_KC);
     a.total_stages = g.N * a.chunks;
@@ -166,17 +190,18 @@ int launch_gw1x1(const Geom& g, const float* gout, const float* x, float* part, 
     const int out_tiles = ceil_div(g.Co, G1_TM) * a.n_ci_tiles;
     if (out_tiles > 65535) return ADDER_ERR_UNSUPPORTED;
     const size_t smem = (size_t)2 * (G1_TM + G1_TN) * G1_PITCH * sizeof(float);
-    const bool vec = (a.HW % 4 == 0) && (((reinterpret_cast<uintptr_t>(gout) | reinterpret_cast<uintptr_t>(x)) & 15) == 0);
+    const bool vec_g = (a.HW % 4 == 0) && ((reinterpret_cast<uintptr_t>(gout) & 15) == 0);
+    const bool vec = vec_g && (gather || (reinterpret_cast<uintptr_t>(x) & 15) == 0);
     const dim3 grid(splits, out_tiles);
-    if (vec) {
-        if (ensure_dynamic_smem(reinterpret_cast<const void*>(adder_gw1x1_kernel<true>), smem) != ADDER_OK)
-            return ADDER_ERR_CUDA;
-        adder_gw1x1_kernel<true><<<grid, G1_THREADS, smem, stream>>>(a);
-    } else {
-        if (ensure_dynamic_smem(reinterpret_cast<const void*>(adder_gw1x1_kernel<false>), smem) != ADDER_OK)
-            return ADDER_ERR_CUDA;
-        adder_gw1x1_kernel<false><<<grid, G1_THREADS, smem, stream>>>(a);
-    }
+    auto run = [&](auto kern) -> int {
+        if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem) != ADDER_OK) return ADDER_ERR_CUDA;
+        kern<<<grid, G1_THREADS, smem, stream>>>(a);
+        return ADDER_OK;
+    };
+    int st;
+    if (gather) st = vec ? run(adder_gw1x1_kernel<true, true>) : run(adder_gw1x1_kernel<false, true>);
+    else st = vec ? run(adder_gw1x1_kernel<true, false>) : run(adder_gw1x1_kernel<false, false>);
+    if (st != ADDER_OK) return st;
     return launched();
 }
 

@@ -40,9 +40,9 @@ __global__ void __launch_bounds__(256, 2) adder_fwd_kernel(const FwdArgs a) {
     const int n0 = tn * a.TI;
     const int ho0 = th * a.TH;
     const int wo_t0 = tw * (a.SPR * RW);      // first output column of this tile
-    const int wi0 = wo_t0 * S - a.g.pad;      // input column of patch column 0
+    const int wi0 = wo_t0 * S * a.pd.GS - a.g.pad;      // input column of patch column 0
     const int co0 = blockIdx.y * (a.CG * RM);
-    const int hi0 = ho0 * S - a.g.pad;       // input row of patch row 0
+    const int hi0 = ho0 * S * a.pd.GS - a.g.pad;       // input row of patch row 0
 
     // thread role: (channel group, segment); segment -> (image, tile row, segment within row)
     uint32_t cg, seg, t2, ws, img, hr;
@@ -303,6 +303,9 @@ static int plan_fwd_t(const Geom& g, const float* out, const TileHint& hint, Fwd
     a.ROWS_PITCH = a.IN_ROWS * a.PITCH;
     a.pd.TI = a.TI; a.pd.ROWS = a.IN_ROWS; a.pd.COLS = a.IN_COLS; a.pd.PITCH = a.PITCH; a.pd.ROWS_PITCH = a.ROWS_PITCH;
     a.pd.d_cols = FastDiv(a.IN_COLS); a.pd.d_rows = FastDiv(a.IN_ROWS);
+    // A strided 1x1 layer is a stride-1 layer on the sampled pixels: the kernel runs its stride-1 form (S = 1)
+    // and the patch fill gathers every g.stride-th row and column, so nothing unsampled is staged.
+    a.pd.GS = (KS == 1 && S == 1) ? g.stride : 1;
     a.CH_STRIDE = a.TI * a.ROWS_PITCH;
     // channel chunk: fill the shared-memory budget (two CTAs per SM) without exceeding Ci
     // shared memory per CTA in proportion to its threads, so that about 16 warps stay resident per SM
@@ -386,7 +389,7 @@ static void choose_fwd_tile(const Geom& g, const TileHint& hint, int& rw, int& r
     if (g.k == 3 && g.stride == 1) { ADDER_FWD_TILES(3, 1, CALL) }                          \
     else if (g.k == 3 && g.stride == 2) { ADDER_FWD_TILES(3, 2, CALL) }                     \
     else if (g.k == 1 && g.stride == 1) { ADDER_FWD_TILES(1, 1, CALL) }                     \
-    else if (g.k == 1 && g.stride == 2) { ADDER_FWD_TILES(1, 2, CALL) }
+    else if (g.k == 1 && g.stride == 2) { ADDER_FWD_TILES(1, 1, CALL) }
 #define ADDER_FWD_TILES(KS_, S_, CALL)                                                      \
     if (rw == 7) { CALL(KS_, S_, 7, 8) }                                                    \
     else if (rw == 8 && rm == 8) { CALL(KS_, S_, 8, 8) }                                    \

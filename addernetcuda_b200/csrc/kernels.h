@@ -48,6 +48,10 @@ struct GxArgs {
     int gs_stage, ws_stage, g1_size, tiles_h, tiles_w, accumulate, class_major;
     FastDiv d_tiles_h, d_tiles_w, d_segs, d_spr, d_sprc, d_th, d_ths, d_ti, d_wpp, d_kk, d_tci;
     int vec_io;          // x is read and grad_x written as aligned quads
+    // A strided 1x1 layer (pad 0) runs as a stride-1 layer on the grid of sampled pixels: `g` then describes that
+    // grid (H = Ho, W = Wo), and x / grad_x are addressed through these strides of the REAL tensor.  samp = 1
+    // (x_plane = H*W, x_row = W) for every other layer.
+    int samp, x_plane, x_row, real_h, real_w, samp_pairs;   // samp_pairs: (value, 0) pairs can be stored as aligned 64-bit words
     int nseg;            // segments per thread: 2 in the paired stride-2 kernel, else 1
     int WPP, wgroups;    // weight staging: pairs per pass and output-channel groups (adder_bwd_input.cu)
     int nstages;         // shared-memory stages: 2 when the output channels take several chunks, else 1

@@ -1,5 +1,5 @@
 // Cooperative asynchronous copy of a zero-filled rectangular patch of an NCHW tensor into shared
-// memory: dst[(c*TI + i)*ROWS_PITCH + r*PITCH + q] = src[n0+i, c0+c, row0+r, col0+q], or 0 where
+// memory: dst[(c*TI + i)*ROWS_PITCH + r*PITCH + q] = src[n0+i, c0+c, row0+r*GS, col0+q*GS], or 0 where
 // any index falls outside the tensor (that is how padding and ragged tile edges are produced).
 #pragma once
 #include "common.cuh"
@@ -9,6 +9,7 @@ namespace adder {
 struct PatchDims {
     int CH, TI, ROWS, COLS, PITCH, ROWS_PITCH;   // patch extents and shared-memory pitches
     int CHS = 0;                                 // channel stride if it is not TI*ROWS_PITCH (padded planes)
+    int GS = 1;                                  // gather stride: patch position (r, q) reads src[row0 + r*GS, col0 + q*GS]
     FastDiv d_cols, d_rows;
 };
 
@@ -29,7 +30,7 @@ __device__ __forceinline__ void fill_patch(float* dst, const float* __restrict__
         uint32_t rho, q, i, r;
         p.d_cols.divmod(e, rho, q);
         p.d_rows.divmod(rho, i, r);
-        const int n = n0 + (int)i, row = row0 + (int)r, col = col0 + (int)q;
+        const int n = n0 + (int)i, row = row0 + (int)r * p.GS, col = col0 + (int)q * p.GS;
         const bool ok = (n < N) & (row >= 0) & (row < Hs) & (col >= 0) & (col < Ws);
         const float* s = ok ? src + ((size_t)(n * C + c0) * plane + row * Ws + col) : src;
         float* d = dst + i * p.ROWS_PITCH + r * p.PITCH + (DUP ? 2 * q : q);

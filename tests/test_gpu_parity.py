@@ -311,6 +311,65 @@ def test_pointwise_stride2_kernels(geom, ac):
         _assert(O.compare("tiled grad_w", ac.backward_weight(gg, xg, wg, 2, 0), want_gws))
 
 
+@pytest.mark.parametrize("geom", [(4, 256, 512, 28, 28), (2, 128, 96, 14, 14), (3, 72, 130, 15, 13), (2, 512, 1024, 8, 6),
+                                  (1, 65, 64, 9, 9)],
+                         ids=lambda t: "n%d_c%dto%d_%dx%d" % t)
+def test_wide_strided_1x1_layers_run_on_the_sampled_grid(geom, ac):
+    """1x1 stride-2 layers too wide for the pointwise kernels (the downsample branches of resnet50.py:84-90):
+    forward, input gradient and weight gradient run their stride-1 forms on the grid of sampled pixels (gather
+    in the fills, scatter with zero fill in the input gradient).  Against the float64 oracle; every input pixel
+    written; accumulate flag; odd plane sizes."""
+    from addernetcuda_b200 import _lib
+    lib = _lib.load()
+    n, ci, co, h, w_ = geom
+    assert "pointwise" not in _lib.describe_plan(0, n, ci, h, w_, co, 1, 2, 0, 0)
+    assert "gemm1x1=1" in _lib.describe_plan(2, n, ci, h, w_, co, 1, 2, 0, 0)
+    gen = torch.Generator().manual_seed(177 + n + ci + co + h)
+    x = torch.randn(n, ci, h, w_, generator=gen)
+    w = torch.randn(co, ci, 1, 1, generator=gen) * 0.7
+    ho, wo = (h - 1) // 2 + 1, (w_ - 1) // 2 + 1
+    g = torch.randn(n, co, ho, wo, generator=gen)
+    want_out = O.adder2d_forward_direct(x, w, 2, 0)
+    want_gx, want_gws, want_gw = O.adder2d_backward_direct(g, x, w, 2, 0)
+    xg, wg, gg = x.to(DEV), w.to(DEV), g.to(DEV)
+    _assert(O.compare("out", ac.forward(xg, wg, 2, 0), want_out))
+    out_s, st = ac.forward(xg, wg, 2, 0, stats=True)
+    _assert(O.compare("out (statistics epilogue)", out_s, want_out))
+    if st.shape[1]:
+        tot = st.sum(1).cpu()
+        ref = want_out.double()
+        assert torch.allclose(tot[:, 0], ref.sum((0, 2, 3)), rtol=1e-5, atol=1e-2)
+    _assert(O.compare("grad_w", ac.backward_weight(gg, xg, wg, 2, 0), want_gws))
+    gw_raw = ac.backward_weight(gg, xg, wg, 2, 0, eta=0.0)
+    scale = max(1.0, float(want_gw.abs().max()))
+    _assert(O.compare("grad_w_unscaled/scale", gw_raw.cpu() / scale, want_gw / scale))
+    mask = torch.zeros(h, w_, dtype=torch.bool, device=DEV)
+    mask[::2, ::2] = True
+    stream = torch.cuda.current_stream().cuda_stream
+    for fast in (False, True):
+        gx = ac.backward_input(gg, xg, wg, 2, 0, fast_clamp=fast)
+        _assert(O.compare("grad_x fast=%d" % fast, gx, want_gx))
+        buf = torch.full_like(xg, float("nan"))
+        flags = _lib.FLAG_FAST_CLAMP if fast else 0
+        args = (gg.data_ptr(), xg.data_ptr(), wg.data_ptr(), buf.data_ptr(), n, ci, h, w_, co, 1, 2, 0)
+        assert lib.adder_b200_backward_input(*args, flags, stream) == 0
+        assert torch.isfinite(buf).all()
+        assert (buf[:, :, ~mask] == 0).all()
+        assert torch.equal(buf, gx)
+        base = torch.randn_like(xg)
+        acc = base.clone()
+        args = args[:3] + (acc.data_ptr(),) + args[4:]
+        assert lib.adder_b200_backward_input(*args, flags | _lib.FLAG_ACCUMULATE, stream) == 0
+        _assert(O.compare("accumulated", acc, (base + gx).cpu()))
+        assert torch.equal(acc[:, :, ~mask], base[:, :, ~mask])
+    # a misaligned gradient buffer takes the element-wise scatter
+    pool = torch.full((xg.numel() + 1,), float("nan"), device=DEV)
+    odd = pool[1:].view_as(xg)
+    args = (gg.data_ptr(), xg.data_ptr(), wg.data_ptr(), odd.data_ptr(), n, ci, h, w_, co, 1, 2, 0)
+    assert lib.adder_b200_backward_input(*args, 0, stream) == 0
+    _assert(O.compare("grad_x into a 4-byte aligned buffer", odd, want_gx))
+
+
 @pytest.mark.parametrize("geom", [(3, 16, 32, 32, 32), (5, 32, 64, 16, 16), (2, 6, 5, 12, 24), (2, 6, 5, 12, 20), (2, 9, 3, 10, 7)],
                          ids=lambda t: "n%d_c%dto%d_%dx%d" % t)
 def test_stride2_paired_input_gradient(geom, ac):
