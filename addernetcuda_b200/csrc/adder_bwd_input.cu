@@ -820,6 +820,7 @@ static int launch_gx_t(const Geom& real, const float* gout, const float* x, cons
 static int choose_gx_rw(const Geom& g, const TileHint& hint) {
     if (hint.rw > 0) return hint.rw;
     const int class_px = ceil_div(g.W, g.stride);
+    if (g.k == 1 && g.H == 1 && g.stride == 1) return 8;     // flattened 1x1 layer or column matrix
     if ((class_px % 8 != 0) && (class_px % 7 == 0)) return 7;
     if (class_px % 4 != 0) return 8;
     if (g.k == 1 && class_px % 8 == 0) return 8;     // one tap per channel: the wider tile halves the loads per term
@@ -837,7 +838,8 @@ static int choose_gx_rw(const Geom& g, const TileHint& hint) {
     else if (rw == 4) { if (fast) { CALL(KS_, S_, 4, 4, true) } else { CALL(KS_, S_, 4, 4, false) } }   \
     else { if (fast) { CALL(KS_, S_, 8, 4, true) } else { CALL(KS_, S_, 8, 4, false) } }
 
-int describe_gx(const Geom& g, int fast, const TileHint& hint, char* buf, size_t n) {
+int describe_gx(const Geom& layer, int fast, const TileHint& hint, char* buf, size_t n) {
+    const Geom g = flatten_pointwise(layer);
     if (hint.is_default() && pointwise_applicable(g)) {
         snprintf(buf, n, "gx k=1 s=%d pointwise fast=%d: one thread per output position, 16 input channels per CTA, threads=256 "
                  "grid=(%d,%d) status=0", g.stride, fast, ceil_div(g.N * g.Ho * g.Wo, 256), ceil_div(g.Ci, 16));
@@ -859,8 +861,9 @@ int describe_gx(const Geom& g, int fast, const TileHint& hint, char* buf, size_t
     return ADDER_OK;
 }
 
-int launch_gx(const Geom& g, const float* gout, const float* x, const float* w, float* gx, int fast,
+int launch_gx(const Geom& layer, const float* gout, const float* x, const float* w, float* gx, int fast,
               int accumulate, const TileHint& hint, cudaStream_t stream) {
+    const Geom g = flatten_pointwise(layer);
     if (hint.is_default() && pointwise_applicable(g)) return launch_pointwise_gx(g, gout, x, w, gx, fast, accumulate, stream);
     const int rw = choose_gx_rw(gx_tiling_geom(g), hint);
 #define ADDER_GX_LAUNCH(KS_, S_, RW_, RC_, FAST_) \

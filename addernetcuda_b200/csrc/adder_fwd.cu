@@ -373,13 +373,14 @@ static int launch_fwd_t(const Geom& g, const float* x, const float* w, float* ou
 // launch has about 16 warps per SM.  Planes that are 7, 14 or 28 wide use 7-pixel segments.
 static void choose_fwd_tile(const Geom& g, const TileHint& hint, int& rw, int& rm) {
     if (hint.rw > 0 && hint.rm > 0) { rw = hint.rw; rm = hint.rm; return; }
-    if ((g.Wo % 8 != 0) && (g.Wo % 7 == 0)) { rw = 7; rm = 8; return; }
+    const bool one_row = (g.k == 1 && g.H == 1);     // flattened 1x1 layer or column matrix: a ragged last segment costs little
+    if (!one_row && (g.Wo % 8 != 0) && (g.Wo % 7 == 0)) { rw = 7; rm = 8; return; }
     if (g.Wo % 4 != 0) { rw = 8; rm = 8; return; }
     const int cand[3][2] = {{8, 8}, {8, 4}, {4, 4}};
     const long long want[3] = {100000, 30000, 0};     // thresholds found by sweeping the ResNet-20 layer shapes
     for (int c = 0; c < 3; ++c) {
         rw = cand[c][0]; rm = cand[c][1];
-        if (g.Wo % rw != 0 && rw == 8) continue;
+        if (g.Wo % rw != 0 && rw == 8 && !one_row) continue;
         const long long threads = (long long)g.N * g.Ho * ceil_div(g.Wo, rw) * ceil_div(g.Co, rm);
         if (threads >= want[c]) return;
     }
@@ -396,7 +397,8 @@ static void choose_fwd_tile(const Geom& g, const TileHint& hint, int& rw, int& r
     else if (rw == 8 && rm == 4) { CALL(KS_, S_, 8, 4) }                                    \
     else if (rw == 4 && rm == 4) { CALL(KS_, S_, 4, 4) }
 
-int describe_fwd(const Geom& g, const TileHint& hint, char* buf, size_t n) {
+int describe_fwd(const Geom& layer, const TileHint& hint, char* buf, size_t n) {
+    const Geom g = flatten_pointwise(layer);
     if (hint.is_default() && pointwise_applicable(g)) {
         snprintf(buf, n, "fwd k=1 s=%d pointwise: one thread per output position, 16 output channels per CTA, threads=256 "
                  "grid=(%d,%d) status=0", g.stride, ceil_div(g.N * g.Ho * g.Wo, 256), ceil_div(g.Co, 16));
@@ -418,7 +420,8 @@ int describe_fwd(const Geom& g, const TileHint& hint, char* buf, size_t n) {
     return ADDER_OK;
 }
 
-int fwd_stat_slices(const Geom& g, const TileHint& hint) {
+int fwd_stat_slices(const Geom& layer, const TileHint& hint) {
+    const Geom g = flatten_pointwise(layer);
     if (hint.is_default() && pointwise_applicable(g)) return 0;
     int rw = 8, rm = 8;
     choose_fwd_tile(g, hint, rw, rm);
@@ -431,8 +434,9 @@ int fwd_stat_slices(const Geom& g, const TileHint& hint) {
     return (int)p.gx;
 }
 
-int launch_fwd(const Geom& g, const float* x, const float* w, float* out, const TileHint& hint,
+int launch_fwd(const Geom& layer, const float* x, const float* w, float* out, const TileHint& hint,
                cudaStream_t stream, double* stats, int stat_slices) {
+    const Geom g = flatten_pointwise(layer);
     if (hint.is_default() && pointwise_applicable(g)) {
         if (stats != nullptr) return ADDER_ERR_UNSUPPORTED;
         return launch_pointwise_fwd(g, x, w, out, stream);
