@@ -30,7 +30,7 @@ def main():
     ap.add_argument("--exact-clamp", action="store_true")
     ap.add_argument("--plain", action="store_true", help="launch only (profiling target)")
     ap.add_argument("--reps", type=int, default=1)
-    ap.add_argument("--legacy", action="store_true", help="the non-persistent kernels (tuning library)")
+    ap.add_argument("--legacy", action="store_true", help="weight gradient by the older pixel-lane tiled kernel (variant 1, through the tuning library)")
     ap.add_argument("--hint", action="append", default=[], metavar="OP:THREADS:CG:TH:TI:CK:SMEMKB",
                     help="tile override for one op (0 forward, 1 grad_x, 2 grad_w), through the tuning library")
     ap.add_argument("--tile", action="append", default=[], metavar="OP:PIXELS:CHANNELS", help="register tile override")
@@ -39,8 +39,7 @@ def main():
         ctx = _lib.tuning()
         tlib = ctx.__enter__()
         if a.legacy:
-            for op in range(3):
-                tlib.adder_b200_set_variant(op, 1)
+            tlib.adder_b200_set_variant(2, 1)
         for h in a.hint:
             v = [int(t) for t in h.split(":")]
             assert tlib.adder_b200_set_tile_hint(*v) == 0

@@ -249,8 +249,8 @@ ADDER_API int adder_b200_set_tile_hint(int op, int threads, int channel_groups, 
 ADDER_API int adder_b200_set_micro_tile(int op, int pixels_per_thread, int channels_per_thread);
 
 /* Kernel family of the weight gradient (op 2; ignored for the other ops): 0 = automatic, 1 = the tiled
- * kernel with pixel lanes everywhere, 2 = the warp-tile kernel that stages with cp.async where the default
- * would use tiled bulk copies. */
+ * kernel with pixel lanes everywhere (also instead of the 1x1 GEMM kernel), 2 = the warp-tile kernel that
+ * stages with cp.async where the default would use tiled bulk copies. */
 ADDER_API int adder_b200_set_variant(int op, int variant);
 #endif /* ADDER_B200_TUNING */
 
