@@ -137,9 +137,9 @@ __device__ __forceinline__ void load_pairs(uint64_t (&dst)[N], const float* __re
 // addresses are a0[l] + row[l] * pitch: the smallest multiple of 4 >= cols (up to +32) minimising,
 // over the four quarter-warps, the worst number of lanes that fall into one 16-byte bank group.
 template <typename F>
-inline int pick_pitch_vec(int cols, int nlanes, F lane_row_and_col) {
+inline int pick_pitch_vec(int cols, int nlanes, F lane_row_and_col, int slack = 32) {
     int best = (cols + 3) / 4 * 4, best_cost = 1 << 30;
-    for (int pitch = (cols + 3) / 4 * 4; pitch <= (cols + 3) / 4 * 4 + 32; pitch += 4) {
+    for (int pitch = (cols + 3) / 4 * 4; pitch <= (cols + 3) / 4 * 4 + slack; pitch += 4) {
         int cost = 0;
         for (int q0 = 0; q0 < nlanes; q0 += 8) {
             int cnt[8] = {0}, worst = 0;
