@@ -18,6 +18,7 @@
 // memory and x' = -x/2 in registers a term costs one saturating add and one fused multiply-add;
 // the correction sum(g) over the same taps is the box sum of the channel-summed g patch, which
 // the CTA accumulates on the side.  The exact variant evaluates the formula as written.
+#include <type_traits>
 #include "common.cuh"
 #include "kernels.h"
 #include "patch_fill.cuh"
@@ -284,15 +285,26 @@ __global__ void __launch_bounds__(256, MB) adder_gx_kernel(const GxArgs a) {
                         }
                     }
                 } else if constexpr (S == 2 && RC == 4) {
+                    // one pass over ALL output channels of the chunk per tap class: the class dispatch is outside
+                    // the channel loop, whose body is then straight-line code (the enclosing loop ends after it)
                     const int ph = (hi + pad) & 1, pwp = ((int)pw + pad) & 1;
                     const int row0 = (hi + pad - ph) / 2 - go_r0;
                     const int col0 = q0 + ((int)pw + pad - pwp) / 2 - go_c0;
+                    auto all_columns = [&](auto PH, auto PW) {
+#pragma unroll 1
+                        for (int cl = 0; cl < ncol; ++cl)
+                            gx_taps_stride2<KS, RW, RC, FAST, decltype(PH)::value, decltype(PW)::value>(
+                                acc, xv, gimg + cl * a.CH_STRIDE, wt + cl * a.WCOL, row0, col0, a.pd.PITCH);
+                    };
+                    using I0 = std::integral_constant<int, 0>;
+                    using I1 = std::integral_constant<int, 1>;
                     switch (ph * 2 + pwp) {     // uniform across a warp when the segments are ordered by class
-                        case 0: gx_taps_stride2<KS, RW, RC, FAST, 0, 0>(acc, xv, gch, wch, row0, col0, a.pd.PITCH); break;
-                        case 1: gx_taps_stride2<KS, RW, RC, FAST, 0, 1>(acc, xv, gch, wch, row0, col0, a.pd.PITCH); break;
-                        case 2: gx_taps_stride2<KS, RW, RC, FAST, 1, 0>(acc, xv, gch, wch, row0, col0, a.pd.PITCH); break;
-                        default: gx_taps_stride2<KS, RW, RC, FAST, 1, 1>(acc, xv, gch, wch, row0, col0, a.pd.PITCH); break;
+                        case 0: all_columns(I0{}, I0{}); break;
+                        case 1: all_columns(I0{}, I1{}); break;
+                        case 2: all_columns(I1{}, I0{}); break;
+                        default: all_columns(I1{}, I1{}); break;
                     }
+                    break;
                 } else {
 #pragma unroll
                     for (int kh = 0; kh < KS; ++kh) {
@@ -428,6 +440,20 @@ __global__ void __launch_bounds__(256, MB) adder_gx_kernel(const GxArgs a) {
     }
 }
 
+// All output channels of one chunk for a thread's two segments whose tap classes are T0 and 3 - T0: the
+// class dispatch happens once per chunk, outside this loop, so the loop body is straight-line code.
+template <int KS, int RW, int RC, bool FAST, int T0>
+__device__ __forceinline__ void gx_s2pair_columns(float (&acc)[2][RC][RW], const float (&xv)[2][RC][RW], const float* gimg,
+                                                  const float* wt, int ncol, int ch_stride, int wcol, const int (&row0v)[2],
+                                                  const int (&col0v)[2], int pitch) {
+    constexpr int T1 = 3 - T0;
+#pragma unroll 1
+    for (int col = 0; col < ncol; ++col, gimg += ch_stride, wt += wcol) {
+        gx_taps_stride2<KS, RW, RC, FAST, (T0 >> 1), (T0 & 1)>(acc[0], xv[0], gimg, wt, row0v[0], col0v[0], pitch);
+        gx_taps_stride2<KS, RW, RC, FAST, (T1 >> 1), (T1 & 1)>(acc[1], xv[1], gimg, wt, row0v[1], col0v[1], pitch);
+    }
+}
+
 // Stride-2 3x3 layers, balanced.  The four classes of input pixels (row offset mod 2, column parity)
 // have 1, 2, 2 and 4 valid taps, so warps that each hold one class finish at very different times and
 // wait for each other at every chunk barrier.  Here a thread owns TWO segments of the same row pair and
@@ -534,6 +560,14 @@ __global__ void __launch_bounds__(256, 2) adder_gx_s2pair_kernel(const GxArgs a)
             const int ncol = min(a.CKO, a.g.Co - c * a.CKO);
             const float* gimg = gs + img * a.pd.ROWS_PITCH;
             const float* wt = Wt + (c & 1) * a.ws_stage + cig * (KK * RC);
+            if (tapcls[1] == 3 - tapcls[0]) {       // always, for pad 1 and tiles that start on even rows
+                switch (tapcls[0]) {                // uniform across a warp
+                    case 0: gx_s2pair_columns<KS, RW, RC, FAST, 0>(acc, xv, gimg, wt, ncol, a.CH_STRIDE, a.WCOL, row0v, col0v, a.pd.PITCH); break;
+                    case 1: gx_s2pair_columns<KS, RW, RC, FAST, 1>(acc, xv, gimg, wt, ncol, a.CH_STRIDE, a.WCOL, row0v, col0v, a.pd.PITCH); break;
+                    case 2: gx_s2pair_columns<KS, RW, RC, FAST, 2>(acc, xv, gimg, wt, ncol, a.CH_STRIDE, a.WCOL, row0v, col0v, a.pd.PITCH); break;
+                    default: gx_s2pair_columns<KS, RW, RC, FAST, 3>(acc, xv, gimg, wt, ncol, a.CH_STRIDE, a.WCOL, row0v, col0v, a.pd.PITCH); break;
+                }
+            } else
 #pragma unroll 1
             for (int col = 0; col < ncol; ++col) {
                 const float* gch = gimg + col * a.CH_STRIDE;
