@@ -42,21 +42,24 @@ __device__ __forceinline__ float gx_term(float wv, float xv) {
 template <int KS, int RW, int RC, bool FAST, int PH, int PW>
 __device__ __forceinline__ void gx_taps_stride2(float (&acc)[RC][RW], const float (&xv)[RC][RW], const float* gch,
                                                 const float* wch, int row0, int col0, int pitch) {
+    constexpr int NKW = (KS - PW + 1) / 2;      // taps of this class along a row: kw = PW, PW + 2, ...
 #pragma unroll
     for (int kh = PH; kh < KS; kh += 2) {
-        const float* gr = gch + (row0 - (kh - PH) / 2) * pitch + col0;
+        // the NKW taps of a row read runs that overlap in all but one value: load their union once
+        const float* gr = gch + (row0 - (kh - PH) / 2) * pitch + col0 - (NKW - 1);
+        float gv[RW + NKW - 1];
 #pragma unroll
-        for (int kw = PW; kw < KS; kw += 2) {
-            const float* gp = gr - (kw - PW) / 2;
-            float gv[RW];
+        for (int j = 0; j < RW + NKW - 1; ++j) gv[j] = gr[j];
 #pragma unroll
-            for (int j = 0; j < RW; ++j) gv[j] = gp[j];
-            const float4 t = *reinterpret_cast<const float4*>(wch + (kh * KS + kw) * RC);
-            const float wv[4] = {t.x, t.y, t.z, t.w};
+        for (int t = 0; t < NKW; ++t) {
+            const int kw = PW + 2 * t;
+            const float4 wq = *reinterpret_cast<const float4*>(wch + (kh * KS + kw) * RC);
+            const float wv[4] = {wq.x, wq.y, wq.z, wq.w};
 #pragma unroll
             for (int cc = 0; cc < RC; ++cc)
 #pragma unroll
-                for (int j = 0; j < RW; ++j) acc[cc][j] = fmaf(gx_term<FAST>(wv[cc], xv[cc][j]), gv[j], acc[cc][j]);
+                for (int j = 0; j < RW; ++j)
+                    acc[cc][j] = fmaf(gx_term<FAST>(wv[cc], xv[cc][j]), gv[NKW - 1 - t + j], acc[cc][j]);
         }
     }
 }
