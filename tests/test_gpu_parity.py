@@ -149,6 +149,35 @@ def test_weight_gradient_kernel_families(case, variant, golden, ac):
         _assert(O.compare("grad_w_unscaled/scale", got_s / scale, want_s / scale))
 
 
+@pytest.mark.parametrize("geom", [(4, 32, 48, 14, 14, 1), (6, 16, 32, 7, 7, 1), (3, 32, 32, 28, 28, 1), (4, 32, 16, 28, 28, 2),
+                                  (5, 16, 64, 14, 14, 2), (2, 64, 32, 13, 27, 2)],
+                         ids=lambda t: "n%d_c%dto%d_%dx%d_s%d" % t)
+def test_warp_tile_weight_gradient_on_imagenet_planes(geom, ac):
+    """Output planes 7, 14 and 28 wide (resnet50.py's stages 2-4) take the warp-tile weight-gradient kernel
+    with 7- or 4-pixel segments; against the float64 oracle, and equal to what the pixel-lane kernel gives."""
+    from addernetcuda_b200 import _lib
+    n, ci, co, h, w_, s = geom
+    plan = _lib.describe_plan(2, n, ci, h, w_, co, 3, s, 1, 0)
+    assert "warp-tile" in plan, plan
+    gen = torch.Generator().manual_seed(311 + n + ci + co + h + s)
+    x = torch.randn(n, ci, h, w_, generator=gen)
+    w = torch.randn(co, ci, 3, 3, generator=gen) * 0.4
+    ho, wo = (h + 2 - 3) // s + 1, (w_ + 2 - 3) // s + 1
+    g = torch.randn(n, co, ho, wo, generator=gen)
+    _, want_gws, want_gw = O.adder2d_backward_direct(g, x, w, s, 1)
+    xg, wg, gg = x.to(DEV), w.to(DEV), g.to(DEV)
+    got = ac.backward_weight(gg, xg, wg, s, 1)
+    _assert(O.compare("grad_w", got, want_gws))
+    raw = ac.backward_weight(gg, xg, wg, s, 1, eta=0.0)
+    scale = max(1.0, float(want_gw.abs().max()))
+    _assert(O.compare("grad_w_unscaled/scale", raw.cpu() / scale, want_gw / scale))
+    assert torch.equal(ac.backward_weight(gg, xg, wg, s, 1), got)        # same bits twice
+    with _lib.tuning() as lib:
+        assert lib.adder_b200_set_variant(2, 1) == 0
+        assert "warp-tile" not in _lib.describe_plan(2, n, ci, h, w_, co, 3, s, 1, 0)
+        _assert(O.compare("pixel-lane kernel", ac.backward_weight(gg, xg, wg, s, 1), want_gws))
+
+
 def test_module_autograd_and_bias(ac):
     from addernetcuda_b200 import adder as A
     from oracle import adder_unfold as U
