@@ -4,6 +4,9 @@
 // the x tile is then gathered with 4-byte copies, everything else is unchanged (GATHER).
 // Both operands are contiguous along p, so tiles [rows][32 pixels] are staged with 16-byte cp.async
 // (4-byte when H*W is not a multiple of 4) and read back with 128-bit loads, four pixels at a time.
+// The (image, pixel) pairs of the whole batch form ONE sequence that is cut into 32-pixel stages wherever
+// they fall, also across image boundaries: a 7x7 plane (49 pixels) would otherwise fill its second stage
+// to 17/32.
 // CTA = 128 threads, output tile 128 co x 64 ci, thread tile 8 x 8 (rows interleaved by 16 / 8 so that
 // the eight lanes of a quarter-warp read consecutive rows: conflict-free with a 36-float pitch).
 // The batch is split over `splits` CTAs per output tile; each writes its slice of partial sums and
@@ -26,9 +29,11 @@ struct Gw1x1Args {
     int N, Co, Ci, HW, splits, stages_per_split, total_stages, chunks, n_ci_tiles;
     int x_plane, x_w, samp;   // GATHER: pixels of an input plane, its row length, sampling stride
     FastDiv d_wo;             // GATHER: divides a pixel index by Wo
+    FastDiv d_hw;             // divides a position of the batch-wide pixel sequence by HW
+    long long total_px;       // N * HW
 };
 
-template <bool VEC, bool GATHER = false>
+template <bool VEC, bool GATHER, bool FLAT>
 __global__ void __launch_bounds__(G1_THREADS, 3) adder_gw1x1_kernel(const Gw1x1Args a) {
     extern __shared__ __align__(16) float smem[];
     constexpr int G_STAGE = G1_TM * G1_PITCH, X_STAGE = G1_TN * G1_PITCH;
@@ -55,53 +60,67 @@ __global__ void __launch_bounds__(G1_THREADS, 3) adder_gw1x1_kernel(const Gw1x1A
         for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
     }
 
+    // Pixel q of stage `st` -> offset of that pixel inside tensor t[N][C][plane] at channel 0.  FLAT: the stages cut
+    // the batch-wide pixel sequence; otherwise every image starts a new stage and (n, k0) are the stage's.
+    int st_n = 0, st_k0 = 0;
+    long long st_kf = 0;
+    auto inside = [&](int q) { return FLAT ? (st_kf + q < a.total_px) : (st_k0 + q < a.HW); };
+    auto locate = [&](int q, int C, int plane, bool gather, size_t& off) {
+        uint32_t n = (uint32_t)st_n, px = (uint32_t)(st_k0 + q);
+        if (FLAT) a.d_hw.divmod((uint32_t)(st_kf + q), n, px);
+        if (gather) {
+            uint32_t ho, wo;
+            a.d_wo.divmod(px, ho, wo);
+            off = (size_t)n * C * plane + (size_t)ho * a.samp * a.x_w + wo * a.samp;
+        } else {
+            off = (size_t)n * C * plane + px;
+        }
+    };
     auto fill = [&](int st, int buf) {
-        const int n = (s_begin + st) / a.chunks, k0 = ((s_begin + st) % a.chunks) * G1_KC;
+        st_kf = (long long)(s_begin + st) * G1_KC;
+        st_n = (s_begin + st) / a.chunks;
+        st_k0 = ((s_begin + st) % a.chunks) * G1_KC;
         float* gd = Gs + buf * G_STAGE;
         float* xd = Xs + buf * X_STAGE;
         if (VEC) {
             for (int e = tid; e < G1_TM * (G1_KC / 4); e += G1_THREADS) {
                 const int r = e >> 3, q = (e & 7) * 4;
-                const bool ok = (co0 + r < a.Co) && (k0 + q < a.HW);
-                const float* src = ok ? a.g + ((size_t)n * a.Co + co0 + r) * a.HW + k0 + q : a.g;
-                cp_async16(gd + r * G1_PITCH + q, src, ok);
+                const bool ok = (co0 + r < a.Co) && inside(q);
+                size_t off = 0;
+                if (ok) locate(q, a.Co, a.HW, false, off);
+                cp_async16(gd + r * G1_PITCH + q, ok ? a.g + off + (size_t)(co0 + r) * a.HW : a.g, ok);
             }
             if (GATHER) {
                 for (int e = tid; e < G1_TN * G1_KC; e += G1_THREADS) {
                     const int r = e >> 5, q = e & 31;
-                    const bool ok = (ci0 + r < a.Ci) && (k0 + q < a.HW);
-                    uint32_t ho, wo;
-                    a.d_wo.divmod(ok ? k0 + q : 0, ho, wo);
-                    const float* src = a.x + ((size_t)n * a.Ci + (ok ? ci0 + r : 0)) * a.x_plane + (size_t)ho * a.samp * a.x_w + wo * a.samp;
-                    cp_async4(xd + r * G1_PITCH + q, ok ? src : a.x, ok);
+                    const bool ok = (ci0 + r < a.Ci) && inside(q);
+                    size_t off = 0;
+                    if (ok) locate(q, a.Ci, a.x_plane, true, off);
+                    cp_async4(xd + r * G1_PITCH + q, ok ? a.x + off + (size_t)(ci0 + r) * a.x_plane : a.x, ok);
                 }
             } else {
-            for (int e = tid; e < G1_TN * (G1_KC / 4); e += G1_THREADS) {
-                const int r = e >> 3, q = (e & 7) * 4;
-                const bool ok = (ci0 + r < a.Ci) && (k0 + q < a.HW);
-                const float* src = ok ? a.x + ((size_t)n * a.Ci + ci0 + r) * a.HW + k0 + q : a.x;
-                cp_async16(xd + r * G1_PITCH + q, src, ok);
-            }
+                for (int e = tid; e < G1_TN * (G1_KC / 4); e += G1_THREADS) {
+                    const int r = e >> 3, q = (e & 7) * 4;
+                    const bool ok = (ci0 + r < a.Ci) && inside(q);
+                    size_t off = 0;
+                    if (ok) locate(q, a.Ci, a.HW, false, off);
+                    cp_async16(xd + r * G1_PITCH + q, ok ? a.x + off + (size_t)(ci0 + r) * a.HW : a.x, ok);
+                }
             }
         } else {
             for (int e = tid; e < G1_TM * G1_KC; e += G1_THREADS) {
                 const int r = e >> 5, q = e & 31;
-                const bool ok = (co0 + r < a.Co) && (k0 + q < a.HW);
-                const float* src = ok ? a.g + ((size_t)n * a.Co + co0 + r) * a.HW + k0 + q : a.g;
-                cp_async4(gd + r * G1_PITCH + q, src, ok);
+                const bool ok = (co0 + r < a.Co) && inside(q);
+                size_t off = 0;
+                if (ok) locate(q, a.Co, a.HW, false, off);
+                cp_async4(gd + r * G1_PITCH + q, ok ? a.g + off + (size_t)(co0 + r) * a.HW : a.g, ok);
             }
             for (int e = tid; e < G1_TN * G1_KC; e += G1_THREADS) {
                 const int r = e >> 5, q = e & 31;
-                const bool ok = (ci0 + r < a.Ci) && (k0 + q < a.HW);
-                const float* src = a.x;
-                if (GATHER) {
-                    uint32_t ho, wo;
-                    a.d_wo.divmod(ok ? k0 + q : 0, ho, wo);
-                    if (ok) src = a.x + ((size_t)n * a.Ci + ci0 + r) * a.x_plane + (size_t)ho * a.samp * a.x_w + wo * a.samp;
-                } else if (ok) {
-                    src = a.x + ((size_t)n * a.Ci + ci0 + r) * a.HW + k0 + q;
-                }
-                cp_async4(xd + r * G1_PITCH + q, src, ok);
+                const bool ok = (ci0 + r < a.Ci) && inside(q);
+                size_t off = 0;
+                if (ok) locate(q, a.Ci, a.x_plane, GATHER, off);
+                cp_async4(xd + r * G1_PITCH + q, ok ? a.x + off + (size_t)(ci0 + r) * a.x_plane : a.x, ok);
             }
         }
     };
@@ -164,10 +183,19 @@ bool gw1x1_applicable(const Geom& g) {
     return g.k == 1 && g.pad == 0 && g.Co >= 64 && g.Ci >= 32 && g.N >= 1;     // any stride: strided layers gather x
 }
 
+// Stages cut the batch-wide pixel sequence (one division more per staged element) where stages that restart with
+// every image would stay more than 8 % empty: 7x7 planes (49 pixels: 23 %) and 14x14 (196: 12.5 %), not 28x28.
+static bool gw1x1_flat(const Geom& g) {
+    const int hw = g.Ho * g.Wo;
+    const int padded = ceil_div(hw, G1_KC) * G1_KC;
+    return (padded - hw) * 100 > 8 * padded;
+}
+
 // Number of batch slices (CTAs per output tile): about three CTAs per SM in total.
 int gw1x1_splits(const Geom& g) {
     const int out_tiles = ceil_div(g.Co, G1_TM) * ceil_div(g.Ci, G1_TN);
-    const int total = g.N * ceil_div(g.Ho * g.Wo, G1_KC);
+    const int total = gw1x1_flat(g) ? (int)(((long long)g.N * g.Ho * g.Wo + G1_KC - 1) / G1_KC)
+                                    : g.N * ceil_div(g.Ho * g.Wo, G1_KC);
     int splits = ceil_div(3 * sm_count(), out_tiles);
     if (splits > total) splits = total;
     if (splits < 1) splits = 1;
@@ -183,8 +211,12 @@ int launch_gw1x1(const Geom& g, const float* gout, const float* x, float* part, 
     a.x_plane = g.H * g.W; a.x_w = g.W; a.samp = g.stride; a.d_wo = FastDiv((uint32_t)g.Wo);
     const bool gather = g.stride != 1;
     a.splits = splits;
+    a.total_px = (long long)g.N * a.HW;
+    if (a.total_px > 2147483647LL) return ADDER_ERR_UNSUPPORTED;
+    a.d_hw = FastDiv((uint32_t)a.HW);
     a.chunks = ceil_div(a.HW, G1_KC);
-    a.total_stages = g.N * a.chunks;
+    const bool flat = gw1x1_flat(g);
+    a.total_stages = flat ? (int)((a.total_px + G1_KC - 1) / G1_KC) : g.N * a.chunks;
     a.stages_per_split = ceil_div(a.total_stages, splits);
     a.n_ci_tiles = ceil_div(g.Ci, G1_TN);
     const int out_tiles = ceil_div(g.Co, G1_TM) * a.n_ci_tiles;
@@ -199,8 +231,13 @@ int launch_gw1x1(const Geom& g, const float* gout, const float* x, float* part, 
         return ADDER_OK;
     };
     int st;
-    if (gather) st = vec ? run(adder_gw1x1_kernel<true, true>) : run(adder_gw1x1_kernel<false, true>);
-    else st = vec ? run(adder_gw1x1_kernel<true, false>) : run(adder_gw1x1_kernel<false, false>);
+    if (flat) {
+        if (gather) st = vec ? run(adder_gw1x1_kernel<true, true, true>) : run(adder_gw1x1_kernel<false, true, true>);
+        else st = vec ? run(adder_gw1x1_kernel<true, false, true>) : run(adder_gw1x1_kernel<false, false, true>);
+    } else {
+        if (gather) st = vec ? run(adder_gw1x1_kernel<true, true, false>) : run(adder_gw1x1_kernel<false, true, false>);
+        else st = vec ? run(adder_gw1x1_kernel<true, false, false>) : run(adder_gw1x1_kernel<false, false, false>);
+    }
     if (st != ADDER_OK) return st;
     return launched();
 }
