@@ -246,6 +246,12 @@ static int plan_fwd_t(const Geom& g, const float* out, const TileHint& hint, Fwd
         // CTA, so that every staged input patch is used twice as often (60 -> 56 us on that layer) - as long as
         // that still leaves about one CTA per SM.
         TileHint h2 = hint;
+        if (KS == 1 && g.Co >= 64) {
+            // 1x1 layers: one tap per staged input value, so twice the channels per CTA pays on every size
+            // (1024->256 14x14: 429 -> 380 us)
+            h2.threads = 256;
+            if (plan_fwd_t<KS, S, RW, RM>(g, out, h2, p) == ADDER_OK) return ADDER_OK;
+        }
         h2.threads = 128;
         const int st = plan_fwd_t<KS, S, RW, RM>(g, out, h2, p);
         if (st == ADDER_OK && p.gx * p.gy < 2LL * sm_count() && g.Co > p.a.TM) {

@@ -31,15 +31,18 @@ def main():
     ap.add_argument("--plain", action="store_true", help="launch only (profiling target)")
     ap.add_argument("--reps", type=int, default=1)
     ap.add_argument("--legacy", action="store_true", help="weight gradient by the older pixel-lane tiled kernel (variant 1, through the tuning library)")
+    ap.add_argument("--gw-variant", type=int, default=0, help="weight-gradient kernel family (1 pixel-lane, 2 warp-tile with cp.async)")
     ap.add_argument("--hint", action="append", default=[], metavar="OP:THREADS:CG:TH:TI:CK:SMEMKB",
                     help="tile override for one op (0 forward, 1 grad_x, 2 grad_w), through the tuning library")
     ap.add_argument("--tile", action="append", default=[], metavar="OP:PIXELS:CHANNELS", help="register tile override")
     a = ap.parse_args()
-    if a.legacy or a.hint or a.tile:
+    if a.legacy or a.hint or a.tile or a.gw_variant:
         ctx = _lib.tuning()
         tlib = ctx.__enter__()
         if a.legacy:
             tlib.adder_b200_set_variant(2, 1)
+        if a.gw_variant:
+            tlib.adder_b200_set_variant(2, a.gw_variant)
         for h in a.hint:
             v = [int(t) for t in h.split(":")]
             assert tlib.adder_b200_set_tile_hint(*v) == 0
