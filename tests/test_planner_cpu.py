@@ -75,7 +75,7 @@ def test_special_case_kernels_are_chosen_where_they_apply():
     # 3x3 stride-2 input gradient: two segments per thread with 4-pixel segments and whole row pairs
     assert "segs/thread=2" in _lib.describe_plan(1, 256, 16, 32, 32, 32, 3, 2, 1, 1)
     assert "segs/thread=1" in _lib.describe_plan(1, 256, 16, 32, 32, 16, 3, 1, 1, 1)
-    assert "segs/thread=1" in _lib.describe_plan(1, 64, 256, 28, 28, 256, 3, 2, 1, 1)          # 7-pixel segments
+    assert "segs/thread=2" in _lib.describe_plan(1, 64, 256, 28, 28, 256, 3, 2, 1, 1)          # ragged last segment
 
 
 def test_chunking_does_not_depend_on_the_batch():
@@ -105,3 +105,27 @@ def test_empty_batch_plans_have_at_least_one_split():
         plan = _lib.describe_plan(2, *shape, 0)
         assert "status=0" in plan and "pointwise=0" in plan, plan
         assert _field(plan, "splits") >= 1, plan
+
+
+def test_imagenet_plane_rules():
+    """Planner rules for the ResNet-50 shapes (resnet50.py:84-90 and the 7/14/28-wide stages): which kernel
+    family and which segment width a geometry gets.  Host-side only: the plans are computed without a GPU."""
+    # 3x3 weight gradient on 28-, 14- and 7-wide planes: warp-tile kernel with 4- or 7-pixel segments
+    for hw, rw in ((28, 4), (14, 7), (7, 7)):
+        plan = _lib.describe_plan(2, 64, 128, hw, hw, 128, 3, 1, 1, 0)
+        assert "warp-tile" in plan and f"RW={rw} " in plan, plan
+    # 56-wide planes take the bulk-copy form
+    assert "tma" in _lib.describe_plan(2, 64, 64, 56, 56, 64, 3, 1, 1, 0)
+    # strided 1x1 layers too wide for the pointwise kernels: stride-1 forms on the sampled grid
+    fwd = _lib.describe_plan(0, 64, 256, 56, 56, 512, 1, 2, 0, 0)
+    assert "pointwise" not in fwd and "s=1" in fwd, fwd
+    assert "gemm1x1=1" in _lib.describe_plan(2, 64, 256, 56, 56, 512, 1, 2, 0, 0)
+    gx = _lib.describe_plan(1, 64, 256, 56, 56, 512, 1, 2, 0, 1)
+    assert "k=1 s=1" in gx and "cols=28" in gx, gx                # tiled over the 28x28 sampled grid
+    # 1x1 stride-1 layers: one row of H*W pixels per image unless the plane is 7n wide
+    assert "cols=3136" in _lib.describe_plan(1, 64, 256, 56, 56, 64, 1, 1, 0, 1) or \
+        "rows=1 " in _lib.describe_plan(1, 64, 256, 56, 56, 64, 1, 1, 0, 1)
+    assert "RW=7" in _lib.describe_plan(1, 64, 1024, 14, 14, 256, 1, 1, 0, 1)
+    # every 3x3 stride-2 input gradient: two complementary segments per thread
+    for hw in (32, 56, 28, 14):
+        assert "segs/thread=2" in _lib.describe_plan(1, 64, 128, hw, hw, 128, 3, 2, 1, 1)
