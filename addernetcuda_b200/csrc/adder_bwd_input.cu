@@ -882,7 +882,7 @@ static int choose_gx_rw(const Geom& g, const TileHint& hint) {
     else { if (fast) { CALL(KS_, S_, 8, 4, true) } else { CALL(KS_, S_, 8, 4, false) } }
 
 int describe_gx(const Geom& layer, int fast, const TileHint& hint, char* buf, size_t n) {
-    const Geom g = flatten_pointwise(layer);
+    const Geom g = flatten_pointwise(layer, true);
     if (hint.is_default() && pointwise_applicable(g)) {
         snprintf(buf, n, "gx k=1 s=%d pointwise fast=%d: one thread per output position, 16 input channels per CTA, threads=256 "
                  "grid=(%d,%d) status=0", g.stride, fast, ceil_div(g.N * g.Ho * g.Wo, 256), ceil_div(g.Ci, 16));
@@ -906,7 +906,7 @@ int describe_gx(const Geom& layer, int fast, const TileHint& hint, char* buf, si
 
 int launch_gx(const Geom& layer, const float* gout, const float* x, const float* w, float* gx, int fast,
               int accumulate, const TileHint& hint, cudaStream_t stream) {
-    const Geom g = flatten_pointwise(layer);
+    const Geom g = flatten_pointwise(layer, true);
     if (hint.is_default() && pointwise_applicable(g)) return launch_pointwise_gx(g, gout, x, w, gx, fast, accumulate, stream);
     const int rw = choose_gx_rw(gx_tiling_geom(g), hint);
 #define ADDER_GX_LAUNCH(KS_, S_, RW_, RC_, FAST_) \

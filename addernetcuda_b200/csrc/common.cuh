@@ -15,9 +15,11 @@ struct Geom {
 // input.  Tiling it as one row of H*W pixels per image gives long runs of aligned 8-pixel segments (56x56
 // planes: input gradient 702 -> 567 us on 256->64 at batch 64).  Planes that are 7, 14 or 28 wide keep
 // their rows: 7-pixel segments, 28 to a warp, measured faster there than 8-pixel segments with a ragged end.
-inline Geom flatten_pointwise(const Geom& g) {
+// (The input gradient also flattens such a plane when H*W is a multiple of 8 - 28x28 - because it then shares a
+// staged value of g between 64 input channels: 512->128 28x28 561 -> 496 us; the forward measured slower that way.)
+inline Geom flatten_pointwise(const Geom& g, bool whole_octets_too = false) {
     Geom f = g;
-    const bool sevens = (g.W % 8 != 0) && (g.W % 7 == 0);
+    const bool sevens = (g.W % 8 != 0) && (g.W % 7 == 0) && !(whole_octets_too && (g.H * g.W) % 8 == 0);
     if (g.k == 1 && g.stride == 1 && g.pad == 0 && g.H > 1 && !sevens && (long long)g.H * g.W <= 2147483647LL) {
         f.W = g.H * g.W; f.H = 1; f.Wo = f.W; f.Ho = 1;
     }
