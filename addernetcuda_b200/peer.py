@@ -18,9 +18,10 @@ import torch.distributed as dist
 
 from . import _lib
 
-# Waits are bounded: a poll costs 32-256 ns, so this is a few seconds - far beyond any skew between ranks
-# inside a training step, short enough that a lost rank surfaces as an error instead of a hang.
-DEFAULT_MAX_POLLS = 1 << 24
+# Waits are bounded: a poll costs 32-256 ns, so this is about fifteen seconds - beyond any skew between the ranks
+# of a healthy job (a rank held up by its host for a moment must not cost the step), short enough that a lost
+# rank surfaces as an error instead of a hang.
+DEFAULT_MAX_POLLS = 1 << 26
 # Buckets above this size stay on NCCL: one-shot moves (world - 1) x the bucket out of every GPU.
 MAX_BUCKET_BYTES = 8 << 20
 
