@@ -184,48 +184,37 @@ constexpr int FIN_OUT = 8;                        // gradient elements per reduc
 constexpr int FIN_LANES = FIN_THREADS / FIN_OUT;  // threads that share one element and split the slices
 constexpr int FUSED_FINISH_MAX = 1 << 17;         // gradients up to this many elements finish in one kernel
 
-// gw[i] = sum_s part[s][i] - w[i] * sum_s gsum_part[s][co(i)], plus the block's partial of sum gw^2.
-// Thread (o, lane) adds the slices lane, lane+8, ... in double precision; the 8 lanes of an element
-// are then added in a fixed order, so the result does not depend on scheduling.
-__global__ void __launch_bounds__(FIN_THREADS) adder_gw_reduce_kernel(const GwFinishArgs a) {
-    __shared__ double s_sum[FIN_LANES][FIN_OUT];
-    __shared__ double s_gs[FIN_LANES][FIN_OUT];
-    __shared__ double s_sq[FIN_OUT];
-    const int o = threadIdx.x & (FIN_OUT - 1);
-    const int lane = threadIdx.x / FIN_OUT;
-    const int i = blockIdx.x * FIN_OUT + o;
-    double s = 0.0, gs = 0.0;
+// gw[i] = sum_s part[s][i] - w[i] * sum_s gsum_part[s][co(i)], plus the block's partial of sum gw^2, in double
+// precision and in slice order, so the result does not depend on scheduling.  This is the form for large
+// gradients (more elements than FUSED_FINISH_MAX), whose slices are few and long: one thread per element, so a
+// warp reads 128 consecutive bytes of every slice.  (Eight elements per block with the block's lanes spread
+// over the slices, as the fused kernel below does for small gradients, took 57 us for the 14 slices of a
+// 1024->256 1x1 layer: 32-byte pieces, most lanes idle.)  The block's 256 squares are added in a fixed order.
+__global__ void __launch_bounds__(FIN_THREADS) adder_gw_reduce_flat_kernel(const GwFinishArgs a) {
+    __shared__ double s_sq[FIN_THREADS];
+    const int i = blockIdx.x * FIN_THREADS + threadIdx.x;
+    double v2 = 0.0;
     if (i < a.CoK) {
         const int co = i / a.K;
         const float* p = a.part + i;
         const float* q = a.gsum_part + co;
-#pragma unroll 4
-        for (int sp = lane; sp < a.splits; sp += FIN_LANES) {
-            s += (double)p[(size_t)sp * a.CoK];
-            gs += (double)q[(size_t)sp * a.Co];
+        double s = 0.0, gs = 0.0;
+#pragma unroll 8
+        for (int sp = 0; sp < a.splits; ++sp) {
+            s += (double)__ldcg(p + (size_t)sp * a.CoK);
+            gs += (double)__ldg(q + (size_t)sp * a.Co);
         }
+        const float vf = (float)(s - (double)a.w[i] * gs);
+        if (a.accumulate) a.gw[i] += vf; else a.gw[i] = vf;
+        v2 = (double)vf * (double)vf;
     }
-    s_sum[lane][o] = s;
-    s_gs[lane][o] = gs;
+    s_sq[threadIdx.x] = v2;
     __syncthreads();
-    if (lane == 0) {
-        double v2 = 0.0;
-        if (i < a.CoK) {
-            double t = 0.0, g = 0.0;
-#pragma unroll
-            for (int l = 0; l < FIN_LANES; ++l) { t += s_sum[l][o]; g += s_gs[l][o]; }
-            const float vf = (float)(t - (double)a.w[i] * g);
-            if (a.accumulate) a.gw[i] += vf; else a.gw[i] = vf;
-            v2 = (double)vf * (double)vf;
-        }
-        s_sq[o] = v2;
+    for (int off = FIN_THREADS / 2; off > 0; off >>= 1) {
+        if ((int)threadIdx.x < off) s_sq[threadIdx.x] += s_sq[threadIdx.x + off];
+        __syncthreads();
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        double t = 0.0;
-        for (int k = 0; k < FIN_OUT; ++k) t += s_sq[k];
-        a.norm_part[blockIdx.x] = (float)t;
-    }
+    if (threadIdx.x == 0) a.norm_part[blockIdx.x] = (float)s_sq[0];
 }
 
 // One block: adds the per-block partial sums of squares in a fixed order and writes
@@ -569,11 +558,12 @@ int launch_gw(const Geom& g, const float* gout, const float* x, const float* w, 
         adder_gw_finish_kernel<<<p.fin_blocks, FIN_THREADS, 0, stream>>>(f, p.fin_blocks, ticket);
         return launched();
     }
-    adder_gw_reduce_kernel<<<p.fin_blocks, FIN_THREADS, 0, stream>>>(f);
+    const int flat_blocks = ceil_div((int)CoK, FIN_THREADS);      // <= fin_blocks: the norm partials fit their array
+    adder_gw_reduce_flat_kernel<<<flat_blocks, FIN_THREADS, 0, stream>>>(f);
     if (launched() != ADDER_OK) return ADDER_ERR_CUDA;
     if (need_norm) {
         float* scale = norm_part + p.fin_blocks;
-        adder_gw_norm_kernel<<<1, 1024, 0, stream>>>(f, p.fin_blocks, scale);
+        adder_gw_norm_kernel<<<1, 1024, 0, stream>>>(f, flat_blocks, scale);
         if (launched() != ADDER_OK) return ADDER_ERR_CUDA;
         if (eta > 0.f) {
             adder_gw_scale_kernel<<<ceil_div((int)CoK, FIN_THREADS), FIN_THREADS, 0, stream>>>(gw, (int)CoK, scale);
