@@ -196,7 +196,9 @@ int gw1x1_splits(const Geom& g) {
     const int out_tiles = ceil_div(g.Co, G1_TM) * ceil_div(g.Ci, G1_TN);
     const int total = gw1x1_flat(g) ? (int)(((long long)g.N * g.Ho * g.Wo + G1_KC - 1) / G1_KC)
                                     : g.N * ceil_div(g.Ho * g.Wo, G1_KC);
-    int splits = ceil_div(3 * sm_count(), out_tiles);
+    // all CTAs in ONE wave of three per SM: rounding up (14 slices x 32 tiles = 448 CTAs for 444 places) sends a
+    // handful of CTAs into a second wave that takes as long as the first
+    int splits = (3 * sm_count()) / out_tiles;
     if (splits > total) splits = total;
     if (splits < 1) splits = 1;
     const int per = ceil_div(total, splits);
