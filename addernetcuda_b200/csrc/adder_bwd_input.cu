@@ -764,7 +764,16 @@ static int plan_gx_n(const Geom& g, const TileHint& hint, GxPlan& p, int nseg) {
     const int budget_floats = (hint.smem_kb > 0 ? hint.smem_kb : (threads_full * nseg <= 64 ? 26 : threads_full * nseg <= 128 ? 52 : 104)) * 1024 / 4;
     int cko = hint.ck > 0 ? hint.ck : (KS == 1 ? 64 : 16);
     if (cko > g.Co) cko = g.Co;
-    while (cko > 1) {
+    // All output channels in ONE chunk need no second stage: where that fits the budget it is taken, whatever the
+    // default chunk size says - no chunk barrier, no running totals, and for 3x3 stride-1 layers the
+    // three-CTAs-per-SM form of the kernel (32->32 16x16).
+    bool whole = false;
+    if (hint.ck <= 0 && KS == 3 && g.Co <= 64) {
+        const int need1 = round_up(g.Co * ti_budget * pd.ROWS_PITCH, 4) + g.Co * a.WCOL +
+                          (FAST ? ti_budget * pd.ROWS_PITCH : 0) + (nseg == 2 ? RC * RW * threads_full * nseg : 0);
+        if (need1 <= budget_floats) { cko = g.Co; whole = true; }
+    }
+    while (cko > 1 && !whole) {
         const int need = 2 * (round_up(cko * ti_budget * pd.ROWS_PITCH, 4) + cko * a.WCOL) +
                          (FAST ? ti_budget * pd.ROWS_PITCH : 0) + RC * RW * threads_full * nseg;
         if (need <= budget_floats) break;
