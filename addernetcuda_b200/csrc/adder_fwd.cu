@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(256, 2) adder_fwd_kernel(const FwdArgs a) {
     constexpr int XW = (RW - 1) * S + KS;   // input values one segment touches per (ci, kh)
     extern __shared__ __align__(16) float smem[];
     float* const Xs = smem;
-    float* const Ws = smem + 2 * a.xs_stage;
+    float* const Ws = smem + a.nstages * a.xs_stage;
 
     const int tid = threadIdx.x;
     const int nthreads = blockDim.x;
@@ -318,7 +318,14 @@ static int plan_fwd_t(const Geom& g, const float* out, const TileHint& hint, Fwd
     const int budget_floats = (hint.smem_kb > 0 ? hint.smem_kb : 100) * 1024 / 4;
     int ck = hint.ck > 0 ? hint.ck : (KS == 1 ? 32 : 16);
     if (ck > g.Ci) ck = g.Ci;
-    while (ck > 1) {
+    // All input channels in ONE chunk need no second stage; where that fits the budget it is taken (no chunk barrier).
+    bool whole = false;
+    if (hint.ck <= 0 && KS == 3 && g.Ci <= 64 &&
+        round_up(g.Ci * ti_budget * a.ROWS_PITCH, 4) + g.Ci * KS * KS * a.TM <= budget_floats) {
+        ck = g.Ci;
+        whole = true;
+    }
+    while (ck > 1 && !whole) {
         const int need = 2 * (round_up(ck * ti_budget * a.ROWS_PITCH, 4) + ck * KS * KS * a.TM);
         if (need <= budget_floats) break;
         --ck;
@@ -330,7 +337,8 @@ static int plan_fwd_t(const Geom& g, const float* out, const TileHint& hint, Fwd
     a.xs_stage = round_up(a.CK * a.CH_STRIDE, 4);
     a.WCIL = a.TM * KS * KS;
     a.ws_stage = a.CK * a.WCIL;
-    size_t smem = (size_t)2 * (a.xs_stage + a.ws_stage) * sizeof(float);
+    a.nstages = a.CK < g.Ci ? 2 : 1;
+    size_t smem = (size_t)a.nstages * (a.xs_stage + a.ws_stage) * sizeof(float);
     const size_t stat_bytes = (size_t)a.TM * a.SEGS * sizeof(float2);   // the statistics epilogue reuses the stages
     if (smem < stat_bytes) smem = stat_bytes;
     p.smem = smem;

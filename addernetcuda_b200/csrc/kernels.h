@@ -31,6 +31,7 @@ struct FwdArgs {
     int TI, TH, SPR, SEGS, CG, TM, TMP, CK;
     int IN_ROWS, IN_COLS, PITCH, ROWS_PITCH, CH_STRIDE;
     int xs_stage, ws_stage, wkk_pad, WCIL, tiles_h, tiles_w, vec_store;
+    int nstages;         // shared-memory stages: 2 when the input channels take several chunks, else 1
     double* stats;       // optional [Co][stat_slices][2]: per pixel tile, the sum of its outputs and of their squares
     int stat_slices, stat_tpc;   // slices = pixel tiles of the launch; tpc = threads that share one channel's reduction
     PatchDims pd;        // haloed input patch staged per input-channel chunk
