@@ -215,6 +215,8 @@ __global__ void __launch_bounds__(256, MB) adder_gx_kernel(const GxArgs a) {
 
     auto fill = [&](int chunk, int stage) {
         const int coc0 = chunk * a.CKO;
+        // (16-byte copies for the halo-free patches of 1x1 layers were measured here and lost 3 % - 256->64 56x56:
+        // 480 -> 498 us - although the same change gains 5 % in the forward kernel)
         fill_patch(Gs + stage * a.gs_stage, a.gout, a.pd, n0, coc0, go_r0, go_c0, a.g.N, a.g.Co, a.g.Ho, a.g.Wo,
                    tid, nthreads);
         gx_stage_weights<KS>(a, Wt + stage * a.ws_stage, coc0, ci0, (int)wgrp, (int)wpr, tid, nthreads);

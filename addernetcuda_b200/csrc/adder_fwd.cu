@@ -64,7 +64,11 @@ __global__ void __launch_bounds__(256, 2) adder_fwd_kernel(const FwdArgs a) {
 
     auto fill = [&](int chunk, int stage) {
         const int ci0 = chunk * a.CK;
-        fill_patch(Xs + stage * a.xs_stage, a.x, a.pd, n0, ci0, hi0, wi0, a.g.N, a.g.Ci, a.g.H, a.g.W, tid, nthreads);
+        if (KS == 1 && a.x_quads)
+            fill_patch_quads(Xs + stage * a.xs_stage, a.x, a.pd, a.d_xquads, n0, ci0, hi0, wi0, a.g.N, a.g.Ci, a.g.H, a.g.W,
+                             tid, nthreads);
+        else
+            fill_patch(Xs + stage * a.xs_stage, a.x, a.pd, n0, ci0, hi0, wi0, a.g.N, a.g.Ci, a.g.H, a.g.W, tid, nthreads);
         float* wsm = Ws + stage * a.ws_stage;
         const int kbase = ci0 * KK;
         const int kk_lim = a.CK * KK;
@@ -312,6 +316,10 @@ static int plan_fwd_t(const Geom& g, const float* out, const TileHint& hint, Fwd
     // A strided 1x1 layer is a stride-1 layer on the sampled pixels: the kernel runs its stride-1 form (S = 1)
     // and the patch fill gathers every g.stride-th row and column, so nothing unsampled is staged.
     a.pd.GS = (KS == 1 && S == 1) ? g.stride : 1;
+    // 1x1 stride-1 layers have no halo: where rows and tiles are whole quads the patch moves in 16-byte copies
+    a.x_quads = (KS == 1 && S == 1 && g.stride == 1 && g.pad == 0 && a.IN_COLS % 4 == 0 && a.PITCH % 4 == 0 && g.W % 4 == 0 &&
+                 (a.SPR * RW) % 4 == 0) ? 1 : 0;
+    a.d_xquads = FastDiv(a.IN_COLS >= 4 ? a.IN_COLS / 4 : 1);
     a.CH_STRIDE = a.TI * a.ROWS_PITCH;
     // channel chunk: fill the shared-memory budget (two CTAs per SM) without exceeding Ci
     // shared memory per CTA in proportion to its threads, so that about 16 warps stay resident per SM
@@ -370,6 +378,7 @@ static int launch_fwd_t(const Geom& g, const float* x, const float* w, float* ou
     const int st = plan_fwd_t<KS, S, RW, RM>(g, out, hint, p);
     if (st != ADDER_OK) return st;
     p.a.x = x; p.a.w = w; p.a.out = out;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) p.a.x_quads = 0;
     if (stats != nullptr) {
         if ((long long)stat_slices != p.gx || p.a.TM * p.a.stat_tpc > p.threads) return ADDER_ERR_WORKSPACE;
         p.a.stats = stats; p.a.stat_slices = stat_slices;

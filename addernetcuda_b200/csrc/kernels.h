@@ -32,6 +32,8 @@ struct FwdArgs {
     int IN_ROWS, IN_COLS, PITCH, ROWS_PITCH, CH_STRIDE;
     int xs_stage, ws_stage, wkk_pad, WCIL, tiles_h, tiles_w, vec_store;
     int nstages;         // shared-memory stages: 2 when the input channels take several chunks, else 1
+    int x_quads;         // 1x1 layers: the halo-free input patch is staged with 16-byte copies
+    FastDiv d_xquads;    // divides by the patch's quads per row
     double* stats;       // optional [Co][stat_slices][2]: per pixel tile, the sum of its outputs and of their squares
     int stat_slices, stat_tpc;   // slices = pixel tiles of the launch; tpc = threads that share one channel's reduction
     PatchDims pd;        // haloed input patch staged per input-channel chunk
